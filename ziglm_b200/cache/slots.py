@@ -85,10 +85,12 @@ class FreeList:
 class GroupPages:
     """Pages of one group of layers: the pool and, per slot, the pages by position."""
 
-    def __init__(self, n_pages: int, page_size: int, window: Optional[int]):
+    def __init__(self, n_pages: int, page_size: int, window: Optional[int], keep_first: int = 0):
+        """``keep_first``: with a window, the first positions of a sequence that stay visible behind it."""
         self.pool = FreeList(n_pages, "page")
         self.page_size = page_size
         self.window = window
+        self.keep_first = max(0, int(keep_first)) if window is not None else 0
         self.pages_of: Dict[int, List[int]] = {}     # slot -> page per block index (-1: released)
         self.table: Optional[np.ndarray] = None      # the same as rows of an int32 array, once its size is known
 
@@ -112,12 +114,14 @@ class GroupPages:
                 self.table[slot, len(pages) - 1] = pages[-1]
 
     def release_behind_window(self, slot: int, length: int) -> None:
-        """Give back pages whose every position lies before the window of the next token."""
+        """Give back pages whose every position lies before the window of the next token, but for the pages that
+        hold the first positions the window keeps."""
         if self.window is None:
             return
         first_visible = max(0, length - self.window + 1)    # the next token sits at position `length`
         pages = self.pages_of.get(slot, [])
-        for i in range(min(len(pages), first_visible // self.page_size)):
+        kept_pages = -(-self.keep_first // self.page_size)
+        for i in range(kept_pages, min(len(pages), first_visible // self.page_size)):
             if pages[i] >= 0:
                 self.pool.give_back(pages[i])
                 pages[i] = -1

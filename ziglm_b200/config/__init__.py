@@ -2,6 +2,7 @@ from .common import ConfigError, read_config_json
 from .llama import LlamaConfig, RopeScaling
 from .tumatar import TumatarConfig
 from .tikalix import TikalixConfig
+from .vilazen import VilazenConfig
 from .registry import (config_from_dict, config_from_folder, register_architecture,
                        registered_architectures, unregister_architecture)
 from .shapes import SHAPES, shape
@@ -9,7 +10,7 @@ from .spec import (FeedForwardSpec, HookSpec, LayerSpec, MixerSpec, ModelSpec, N
                    PositionSpec)
 
 __all__ = [
-    "ConfigError", "LlamaConfig", "TumatarConfig", "TikalixConfig", "SHAPES", "shape", "RopeScaling", "read_config_json",
+    "ConfigError", "LlamaConfig", "TumatarConfig", "TikalixConfig", "VilazenConfig", "SHAPES", "shape", "RopeScaling", "read_config_json",
     "config_from_dict", "config_from_folder", "register_architecture",
     "registered_architectures", "unregister_architecture",
     "FeedForwardSpec", "HookSpec", "LayerSpec", "MixerSpec", "ModelSpec", "NormSpec", "PositionSpec",

@@ -16,6 +16,7 @@ from .common import ConfigError, architecture_name, read_config_json
 from .llama import LlamaConfig
 from .tumatar import TumatarConfig
 from .tikalix import TikalixConfig
+from .vilazen import VilazenConfig
 from .spec import ModelSpec
 
 _ARCHITECTURES: Dict[str, Any] = {}
@@ -66,3 +67,4 @@ def config_from_folder(folder: str):
 register_architecture(LlamaConfig.ARCHITECTURE, LlamaConfig)
 register_architecture(TumatarConfig.ARCHITECTURE, TumatarConfig)
 register_architecture(TikalixConfig.ARCHITECTURE, TikalixConfig)
+register_architecture(VilazenConfig.ARCHITECTURE, VilazenConfig)

@@ -439,7 +439,8 @@ __device__ __forceinline__ float fold_value(float o, float a, float op, float b)
 template <typename T, int VEC, int G, int NREG>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restrict__ out, int n_heads, int n_kv,
-                         int hd, float scale, float softcap, int window, const int* __restrict__ positions,
+                         int hd, float scale, float softcap, int window, int keep_first,
+                         const float* __restrict__ sinks, const int* __restrict__ positions,
                          const int* __restrict__ seq_of_token, const int* __restrict__ block_table, int bt_stride,
                          const T* __restrict__ k_pages, const T* __restrict__ v_pages, int page_size,
                          long page_stride, float* __restrict__ part_ml, float* __restrict__ part_o, int max_parts) {
@@ -453,7 +454,9 @@ attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restri
     const int b = seq_of_token[t];
     const int kvh = h0 / (n_heads / n_kv);
     const int start = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int n_keys = pos - start + 1;
+    // the keys a token sees, counted through: the first tokens a window keeps (those before the window), then the window
+    const int kept = min(keep_first, start);
+    const int n_keys = kept + pos - start + 1;
     const int n_parts = (n_keys + ATT_PART - 1) / ATT_PART;
     const bool split = part_o != nullptr;
     const int p_lo = split ? (int)blockIdx.z : 0, p_hi = split ? min(n_parts, (int)blockIdx.z + 1) : n_parts;
@@ -482,13 +485,13 @@ attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restri
 #pragma unroll
             for (int i = 0; i < NREG; ++i) acc[g][i] = 0.f;
         }
-        const int part_first = start + part * ATT_PART;
+        const int part_first = part * ATT_PART;
 #pragma unroll 1
         for (int kb = warp; kb < 2 * ATT_WARPS; kb += ATT_WARPS) {
             const int first = part_first + kb * 32;
-            if (first > pos) break;                              // uniform per warp
-            const int j = first + lane;
-            const bool valid = j <= pos;
+            if (first >= n_keys) break;                          // uniform per warp
+            const bool valid = first + lane < n_keys;
+            const int j = first + lane < kept ? first + lane : start + (first + lane - kept);
             float sc[G];
 #pragma unroll
             for (int g = 0; g < G; ++g) sc[g] = 0.f;
@@ -522,7 +525,7 @@ attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restri
 #pragma unroll
                 for (int i = 0; i < NREG; ++i) acc[g][i] *= corr;
             }
-            const int n_valid = min(32, pos - first + 1);
+            const int n_valid = min(32, n_keys - first);
 #pragma unroll 4
             for (int jj = 0; jj < n_valid; ++jj) {
                 const long voff = __shfl_sync(0xffffffffu, row_off, jj);
@@ -587,6 +590,17 @@ attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restri
         }
     }
     if (split) return;
+    if (sinks != nullptr) {
+        // a number in the softmax's denominator that belongs to no key: one more fold, with no values
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float a, bb, m_new;
+            fold_weights(run_m[g], sinks[h0 + g], m_new, a, bb);
+#pragma unroll
+            for (int r = 0; r < NRUN; ++r) run_o[g][r] = fold_value(run_o[g][r], a, 0.f, bb);
+            run_l[g] = fold_value(run_l[g], a, 1.0f, bb);
+        }
+    }
 #pragma unroll
     for (int g = 0; g < G; ++g)
 #pragma unroll
@@ -599,12 +613,13 @@ attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restri
 // grid (T, n_heads), 128 threads: folds the parts a split launch left in scratch memory, in ascending order.
 template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
-attention_fold_kernel(T* __restrict__ out, int n_heads, int hd, int window, const int* __restrict__ positions,
+attention_fold_kernel(T* __restrict__ out, int n_heads, int hd, int window, int keep_first,
+                      const float* __restrict__ sinks, const int* __restrict__ positions,
                       const float* __restrict__ part_ml, const float* __restrict__ part_o, int max_parts) {
     const int t = blockIdx.x, h = blockIdx.y;
     const int pos = positions[t];
     const int start = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-    const int n_parts = (pos - start + 1 + ATT_PART - 1) / ATT_PART;
+    const int n_parts = (min(keep_first, start) + pos - start + 1 + ATT_PART - 1) / ATT_PART;
     const float* ml = part_ml + ((long)t * n_heads + h) * max_parts * 2;
     const float* po = part_o + ((long)t * n_heads + h) * max_parts * hd;
     constexpr int NRUN = ATT_MAX_HD / (ATT_WARPS * 32);
@@ -620,6 +635,13 @@ attention_fold_kernel(T* __restrict__ out, int n_heads, int hd, int window, cons
         run_l = fold_value(run_l, a, ml[2 * part + 1], bb);
         run_m = m_new;
     }
+    if (sinks != nullptr) {
+        float a, bb, m_new;
+        fold_weights(run_m, sinks[h], m_new, a, bb);
+#pragma unroll
+        for (int r = 0; r < NRUN; ++r) run_o[r] = fold_value(run_o[r], a, 0.f, bb);
+        run_l = fold_value(run_l, a, 1.0f, bb);
+    }
 #pragma unroll
     for (int r = 0; r < NRUN; ++r) {
         const int d = threadIdx.x + r * ATT_WARPS * 32;
@@ -629,13 +651,14 @@ attention_fold_kernel(T* __restrict__ out, int n_heads, int hd, int window, cons
 
 template <typename T, int VEC, int G>
 static int launch_attention(const void* q, long q_row_stride, void* out, int T_, int n_heads, int n_kv, int hd, float scale,
-                            float softcap, int window, const int* positions, const int* seq_of_token, const int* block_table,
+                            float softcap, int window, int keep_first, const float* sinks, const int* positions,
+                            const int* seq_of_token, const int* block_table,
                             int bt_stride, const void* k_pages, const void* v_pages, int page_size, long page_stride,
                             float* part_ml, float* part_o, int max_parts, cudaStream_t stream) {
     dim3 grid(T_, n_heads / G, part_o ? max_parts : 1);
 #define ZLM_ATT_GO(NREG)                                                                                              \
     attention_general_kernel<T, VEC, G, NREG><<<grid, ATT_WARPS * 32, 0, stream>>>(                                     \
-        (const T*)q, q_row_stride, (T*)out, n_heads, n_kv, hd, scale, softcap, window, positions, seq_of_token, block_table, \
+        (const T*)q, q_row_stride, (T*)out, n_heads, n_kv, hd, scale, softcap, window, keep_first, sinks, positions, seq_of_token, block_table, \
         bt_stride, (const T*)k_pages, (const T*)v_pages, page_size, page_stride, part_ml, part_o, max_parts)
     if (hd <= 128) ZLM_ATT_GO(4);
     else if (hd <= 256) ZLM_ATT_GO(8);
@@ -643,24 +666,131 @@ static int launch_attention(const void* q, long q_row_stride, void* out, int T_,
 #undef ZLM_ATT_GO
     int rc = launch_status();
     if (rc || !part_o) return rc;
-    attention_fold_kernel<T><<<dim3(T_, n_heads), ATT_WARPS * 32, 0, stream>>>((T*)out, n_heads, hd, window, positions,
-                                                                           part_ml, part_o, max_parts);
+    attention_fold_kernel<T><<<dim3(T_, n_heads), ATT_WARPS * 32, 0, stream>>>((T*)out, n_heads, hd, window, keep_first, sinks,
+                                                                           positions, part_ml, part_o, max_parts);
     return launch_status();
 }
 
 template <typename T, int VEC>
 static int pick_group(int group, const void* q, long q_row_stride, void* out, int T_, int n_heads, int n_kv, int hd,
-                      float scale, float softcap, int window, const int* positions, const int* seq_of_token, const int* block_table,
+                      float scale, float softcap, int window, int keep_first, const float* sinks, const int* positions,
+                      const int* seq_of_token, const int* block_table,
                       int bt_stride, const void* k_pages, const void* v_pages, int page_size, long page_stride,
                       float* part_ml, float* part_o, int max_parts, cudaStream_t stream) {
 #define ZLM_ATT(GV)                                                                                                     \
-    launch_attention<T, VEC, GV>(q, q_row_stride, out, T_, n_heads, n_kv, hd, scale, softcap, window, positions, seq_of_token, \
+    launch_attention<T, VEC, GV>(q, q_row_stride, out, T_, n_heads, n_kv, hd, scale, softcap, window, keep_first, sinks, positions, seq_of_token, \
                                  block_table, bt_stride, k_pages, v_pages, page_size, page_stride, part_ml, part_o,     \
                                  max_parts, stream)
     if (group % 4 == 0 && hd <= 256) return ZLM_ATT(4);
     if (group % 2 == 0) return ZLM_ATT(2);
     return ZLM_ATT(1);
 #undef ZLM_ATT
+}
+
+// What stands between the q|k|v product and attention in a mixer whose q and k are normed as whole vectors: one
+// block per token.  In order: (1) with norm weights, q (all heads as one vector) and k (likewise) are each divided by
+// the root of (their mean square + eps) and multiplied by their weight, element by element; n_q / n_k are the counts
+// the means are taken over (heads kept with zeros behind them have fewer true elements than hd a head); (2) the first
+// `rot` dimensions of every q and k head are turned by the token's position, pairs (i, i + rot/2); (3) the values are
+// mixed with those another layer left for the same tokens, v <- (1 - mix) v + mix v_other (mix_mode 2), or left there
+// for later layers (mix_mode 1); (4) q, k, v are written back and k, v stored in the cache pages.  Everything between
+// the read and the write is float.
+// Rows: [q: n_heads*hd | k: n_kv*hd | v: n_kv*hd | anything else]; mix_buf: [T, n_kv*v_dim] contiguous, in the rows'
+// type: the first v_dim elements of every value head (the rest of a head is zeros it is kept with).
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_prep_kernel(T* __restrict__ qkv, long row_stride, int n_heads, int n_kv, int hd, int rot,
+               const float* __restrict__ inv_freq, const float* __restrict__ q_w, const float* __restrict__ k_w,
+               int n_q, int n_k, float norm_eps, int mix_mode, float mix, T* __restrict__ mix_buf, int v_dim,
+               const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+               const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_pages, T* __restrict__ v_pages,
+               int page_size, long page_stride) {
+    __shared__ float cos_s[ROPE_MAX_HALF], sin_s[ROPE_MAX_HALF];
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = rot / 2;
+    const bool turn = inv_freq != nullptr && half > 0;
+    if (turn)
+        for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sin_s[i], &cos_s[i]);
+    T* row0 = qkv + (long)t * row_stride;
+    const int q_len = n_heads * hd, k_len = n_kv * hd;
+    float inv_q = 1.0f, inv_k = 1.0f;
+    if (q_w != nullptr) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < q_len; i += blockDim.x) { const float v = to_float(row0[i]); ss = fmaf(v, v, ss); }
+        inv_q = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n_q + norm_eps);
+    }
+    if (k_w != nullptr) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < k_len; i += blockDim.x) { const float v = to_float(row0[q_len + i]); ss = fmaf(v, v, ss); }
+        inv_k = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n_k + norm_eps);
+    }
+    __syncthreads();
+    T* kdst = nullptr;
+    T* vdst = nullptr;
+    if (k_pages != nullptr && n_kv > 0) {
+        const int b = seq_of_token[t];
+        const int page = block_table[(long)b * bt_stride + pos / page_size];
+        const long off = (long)page * page_stride + (long)(pos % page_size) * hd;
+        kdst = k_pages + off;       // head h of the cache row lies h * page_size * hd further
+        vdst = v_pages + off;
+    }
+    const long kv_head_stride = (long)page_size * hd;
+    const int qk_heads = n_heads + n_kv;
+    if (turn) {
+        for (int idx = threadIdx.x; idx < qk_heads * half; idx += blockDim.x) {
+            const int head = idx / half, i = idx - head * half;
+            const bool is_k = head >= n_heads;
+            const int at = head * hd + i;                   // q and k heads lie one behind the other
+            float a = to_float(row0[at]), b2 = to_float(row0[at + half]);
+            const float* w = is_k ? k_w : q_w;
+            if (w != nullptr) {
+                const int wi = at - (is_k ? q_len : 0);
+                const float inv = is_k ? inv_k : inv_q;
+                a = (a * inv) * w[wi];
+                b2 = (b2 * inv) * w[wi + half];
+            }
+            const float c = cos_s[i], sn = sin_s[i];
+            const T lo = from_float<T>(a * c - b2 * sn), hi = from_float<T>(b2 * c + a * sn);
+            row0[at] = lo;
+            row0[at + half] = hi;
+            if (kdst && is_k) {
+                T* d = kdst + (long)(head - n_heads) * kv_head_stride;
+                d[i] = lo;
+                d[i + half] = hi;
+            }
+        }
+    }
+    const int first_rest = turn ? rot : 0, rest = hd - first_rest;
+    for (int idx = threadIdx.x; idx < qk_heads * rest; idx += blockDim.x) {
+        const int head = idx / rest, i = first_rest + (idx - head * rest);
+        const bool is_k = head >= n_heads;
+        const float* w = is_k ? k_w : q_w;
+        if (w == nullptr && !(kdst && is_k)) continue;      // nothing changes and nothing is stored
+        const int at = head * hd + i;
+        float a = to_float(row0[at]);
+        if (w != nullptr) a = (a * (is_k ? inv_k : inv_q)) * w[at - (is_k ? q_len : 0)];
+        const T o = from_float<T>(a);
+        row0[at] = o;
+        if (kdst && is_k) kdst[(long)(head - n_heads) * kv_head_stride + i] = o;
+    }
+    T* vrow = row0 + q_len + k_len;
+    for (int idx = threadIdx.x; idx < k_len; idx += blockDim.x) {
+        const int g = idx / hd, i = idx - g * hd;
+        T o = vrow[idx];
+        if (mix_mode != 0 && i < v_dim) {                    // what lies behind a head's v_dim values is zero and stays
+            const long at = ((long)t * n_kv + g) * v_dim + i;
+            if (mix_mode == 1) mix_buf[at] = o;
+            else {
+                o = from_float<T>((1.0f - mix) * to_float(o) + mix * to_float(mix_buf[at]));
+                vrow[idx] = o;
+            }
+        }
+        if (vdst) vdst[(long)g * kv_head_stride + i] = o;
+    }
 }
 
 }  // namespace zlm
@@ -766,16 +896,21 @@ ZLM_EXPORT long zlm_attention_general_scratch(int T, int n_heads, int n_kv, int 
     return (long)T * n_heads * parts * (hd + 2);
 }
 
+// keep_first (with a window): the first keep_first positions of a sequence stay visible behind the window.  sinks (float,
+// one per query head; may be null): exp(sinks[h]) is added to the softmax's denominator of head h; it has no key and no
+// value and is not scaled.
 // max_keys: the most keys any token of the step sees.  scratch (float, scratch_floats elements; may be null):
 // when it holds at least zlm_attention_general_scratch(...) floats and that is not 0, the parts of the keys are
 // computed by blocks of their own and folded by a second kernel; the result is bit for bit the same.
 ZLM_EXPORT int zlm_attention_general(const void* q, long q_row_stride, void* out, int dtype, int T, int n_heads,
-                                     int n_kv, int hd, float scale, float softcap, int window, const int* positions,
+                                     int n_kv, int hd, float scale, float softcap, int window, int keep_first,
+                                     const float* sinks, const int* positions,
                                      const int* seq_of_token, const int* block_table, int bt_stride,
                                      const void* k_pages, const void* v_pages, int page_size, long page_stride,
                                      int max_keys, float* scratch, long scratch_floats, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size <= 0) return ZLM_ERR_BAD_ARG;
+    if (n_heads <= 0 || n_kv <= 0 || n_heads % n_kv || page_size <= 0 || keep_first < 0) return ZLM_ERR_BAD_ARG;
+    if (window <= 0) keep_first = 0;
     if (hd <= 0 || hd > ATT_MAX_HD || hd % 8) return ZLM_ERR_UNSUPPORTED;
     float *part_ml = nullptr, *part_o = nullptr;
     int max_parts = 1;
@@ -788,12 +923,43 @@ ZLM_EXPORT int zlm_attention_general(const void* q, long q_row_stride, void* out
     }
     const int group = n_heads / n_kv;
     if (dtype == ZLM_F32)
-        return pick_group<float, 4>(group, q, q_row_stride, out, T, n_heads, n_kv, hd, scale, softcap, window, positions,
-                                    seq_of_token, block_table, bt_stride, k_pages, v_pages, page_size, page_stride,
+        return pick_group<float, 4>(group, q, q_row_stride, out, T, n_heads, n_kv, hd, scale, softcap, window, keep_first, sinks,
+                                    positions, seq_of_token, block_table, bt_stride, k_pages, v_pages, page_size, page_stride,
                                     part_ml, part_o, max_parts, stream);
     if (dtype == ZLM_BF16)
-        return pick_group<__nv_bfloat16, 8>(group, q, q_row_stride, out, T, n_heads, n_kv, hd, scale, softcap, window, positions,
-                                            seq_of_token, block_table, bt_stride, k_pages, v_pages, page_size,
+        return pick_group<__nv_bfloat16, 8>(group, q, q_row_stride, out, T, n_heads, n_kv, hd, scale, softcap, window, keep_first,
+                                            sinks, positions, seq_of_token, block_table, bt_stride, k_pages, v_pages, page_size,
                                             page_stride, part_ml, part_o, max_parts, stream);
     return ZLM_ERR_UNSUPPORTED;
+}
+
+// See qk_prep_kernel.  q_w / k_w: float norm weights laid out like the q and the k heads of a row (null: that vector is
+// not normed); n_q / n_k: the element counts of the means.  mix_mode 0: values as they are; 1: also left in mix_buf;
+// 2: mixed with mix_buf ([T, n_kv * v_dim]: the true values of every head).  k_pages == nullptr: nothing is stored.
+ZLM_EXPORT int zlm_qk_prep(void* qkv, int dtype, long row_stride, int T, int n_heads, int n_kv, int hd, int rot,
+                           const float* inv_freq, const float* q_w, const float* k_w, int n_q, int n_k, float norm_eps,
+                           int mix_mode, float mix, void* mix_buf, int v_dim, const int* positions, const int* seq_of_token,
+                           const int* block_table, int bt_stride, void* k_pages, void* v_pages, int page_size,
+                           long page_stride, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (hd <= 0 || rot < 0 || rot > hd || (rot & 1) || n_heads <= 0 || n_kv <= 0 || page_size <= 0 || mix_mode < 0 ||
+        mix_mode > 2 || (mix_mode != 0 && (mix_buf == nullptr || v_dim <= 0 || v_dim > hd)) || (k_pages != nullptr && v_pages == nullptr) ||
+        (q_w != nullptr && n_q <= 0) || (k_w != nullptr && n_k <= 0))
+        return ZLM_ERR_BAD_ARG;
+    if (rot / 2 > ROPE_MAX_HALF) return ZLM_ERR_UNSUPPORTED;
+    const int work = (n_heads + 2 * n_kv) * hd;
+    const int threads = work >= 2048 ? 256 : (work >= 512 ? 128 : 64);
+    cudaError_t e;
+    if (dtype == ZLM_F32)
+        e = launch_pdl(qk_prep_kernel<float>, dim3(T), dim3(threads), 0, stream, (float*)qkv, row_stride, n_heads, n_kv, hd,
+                       rot, inv_freq, q_w, k_w, n_q, n_k, norm_eps, mix_mode, mix, (float*)mix_buf, v_dim, positions, seq_of_token,
+                       block_table, bt_stride, (float*)k_pages, (float*)v_pages, page_size, page_stride);
+    else if (dtype == ZLM_BF16)
+        e = launch_pdl(qk_prep_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (__nv_bfloat16*)qkv, row_stride,
+                       n_heads, n_kv, hd, rot, inv_freq, q_w, k_w, n_q, n_k, norm_eps, mix_mode, mix, (__nv_bfloat16*)mix_buf,
+                       v_dim, positions, seq_of_token, block_table, bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages,
+                       page_size, page_stride);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
 }

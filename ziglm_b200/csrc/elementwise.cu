@@ -307,15 +307,17 @@ __global__ void norm_add_scaled_kernel(const float* __restrict__ branch, const T
     }
 }
 
-// out[i] = act(x[i]); kind 0: the squared relu, max(x, 0)^2
+// out[i] = act(x[i]); kind 0: the squared relu, max(x, 0)^2; kind 1: the exact gelu, x (1 + erf(x / sqrt 2)) / 2
 template <typename T>
 __global__ void unary_act_kernel(const T* __restrict__ x, T* __restrict__ out, long n, int kind) {
     pdl_launch_dependents();
     pdl_wait();
     const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const float v = fmaxf(to_float(x[i]), 0.f);
-    out[i] = from_float<T>(v * v);
+    float v = to_float(x[i]);
+    if (kind == 1) v = 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+    else { v = fmaxf(v, 0.f); v *= v; }
+    out[i] = from_float<T>(v);
 }
 
 // out[t, i] = a[t, i] * sigmoid(g[t, i]) over rows with strides of their own (a gate on the heads' outputs)
@@ -351,6 +353,55 @@ __global__ void sigmoid_mul_vec_kernel(const __nv_bfloat16* __restrict__ a, long
         ap[k] = __floats2bfloat162_rn(x.x * (1.0f / (1.0f + expf(-y.x))), x.y * (1.0f / (1.0f + expf(-y.y))));
     }
     *reinterpret_cast<uint4*>(out + t * out_stride + i) = av;
+}
+
+// out[t, i] = in[t, i] over rows with strides of their own, from one storage type to another
+template <typename TI, typename TO>
+__global__ void convert_rows_kernel(const TI* __restrict__ in, long in_stride, TO* __restrict__ out, long out_stride,
+                                    long total, int n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long t = idx / n;
+    const int i = (int)(idx - t * n);
+    out[t * out_stride + i] = from_float<TO>(to_float(in[t * in_stride + i]));
+}
+
+// out[t, h * n + i] = a[t, h * n + i] * sigmoid(g[t, h]) * mult over rows with strides of their own: one gate a head.
+template <typename T>
+__global__ void gate_heads_kernel(const T* __restrict__ a, long a_stride, const T* __restrict__ g, long g_stride,
+                                  T* __restrict__ out, long out_stride, long total, int heads, int n, float mult) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int width = heads * n;
+    const long t = idx / width;
+    const int i = (int)(idx - t * width);
+    const float gv = to_float(g[t * g_stride + i / n]);
+    out[t * out_stride + i] = from_float<T>(to_float(a[t * a_stride + i]) * ((1.0f / (1.0f + expf(-gv))) * mult));
+}
+
+// out[r, i] = x[r, i] / sqrt(mean_i x[r, i]^2 + eps) * w[i] * sigmoid(g[r, i]) * mult: the norm over the concatenated
+// heads of a mixer and its output gate in one pass.  x float rows, g and out rows of the step's type, all with strides
+// of their own.
+template <typename T>
+__global__ void norm_gate_kernel(const float* __restrict__ x, long x_stride, const float* __restrict__ w,
+                                 const T* __restrict__ g, long g_stride, T* __restrict__ out, long out_stride, int d,
+                                 float eps, float mult) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* xr = x + (long)blockIdx.x * x_stride;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += blockDim.x) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+        float y = (xr[i] * inv) * w[i];
+        if (g != nullptr) y *= 1.0f / (1.0f + expf(-to_float(g[(long)blockIdx.x * g_stride + i])));
+        out[(long)blockIdx.x * out_stride + i] = from_float<T>(y * mult);
+    }
 }
 
 template <typename TW>
@@ -603,10 +654,10 @@ ZLM_EXPORT int zlm_norm_add_scaled(const float* branch, const void* w, int w_dty
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 
-// kind 0: the squared relu.  out may be x.
+// kind 0: the squared relu, 1: the exact gelu.  out may be x.
 ZLM_EXPORT int zlm_unary_act(const void* x, void* out, int dtype, long n, int kind, cudaStream_t stream) {
     if (n <= 0) return 0;
-    if (kind != 0) return ZLM_ERR_BAD_ARG;
+    if (kind != 0 && kind != 1) return ZLM_ERR_BAD_ARG;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     cudaError_t e;
     if (dtype == ZLM_F32)
@@ -637,6 +688,61 @@ ZLM_EXPORT int zlm_sigmoid_mul(const void* a, long a_stride, const void* g, long
     else if (dtype == ZLM_BF16)
         e = launch_pdl(sigmoid_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)a,
                        a_stride, (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride, total, n);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+// out rows = in rows, converted; T rows of n elements, each operand with its own row stride.
+ZLM_EXPORT int zlm_convert_rows(const void* in, int in_dtype, long in_stride, void* out, int out_dtype, long out_stride,
+                                int T, int n, cudaStream_t stream) {
+    if (T <= 0 || n <= 0) return 0;
+    const long total = (long)T * n;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaError_t e;
+#define ZLM_CR(TI, TO)                                                                                              \
+    e = launch_pdl(convert_rows_kernel<TI, TO>, dim3(blocks), dim3(256), 0, stream, (const TI*)in, in_stride, (TO*)out, \
+                   out_stride, total, n)
+    if (in_dtype == ZLM_F32 && out_dtype == ZLM_F32) ZLM_CR(float, float);
+    else if (in_dtype == ZLM_F32 && out_dtype == ZLM_BF16) ZLM_CR(float, __nv_bfloat16);
+    else if (in_dtype == ZLM_BF16 && out_dtype == ZLM_F32) ZLM_CR(__nv_bfloat16, float);
+    else if (in_dtype == ZLM_BF16 && out_dtype == ZLM_BF16) ZLM_CR(__nv_bfloat16, __nv_bfloat16);
+    else return ZLM_ERR_UNSUPPORTED;
+#undef ZLM_CR
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+// out[t, h * n + i] = a[t, h * n + i] * sigmoid(g[t, h]) * mult; T rows, every operand with its own row stride.
+ZLM_EXPORT int zlm_gate_heads(const void* a, long a_stride, const void* g, long g_stride, void* out, long out_stride,
+                              int dtype, int T, int heads, int n, float mult, cudaStream_t stream) {
+    if (T <= 0 || heads <= 0 || n <= 0) return 0;
+    const long total = (long)T * heads * n;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaError_t e;
+    if (dtype == ZLM_F32)
+        e = launch_pdl(gate_heads_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)a, a_stride,
+                       (const float*)g, g_stride, (float*)out, out_stride, total, heads, n, mult);
+    else if (dtype == ZLM_BF16)
+        e = launch_pdl(gate_heads_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)a, a_stride,
+                       (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride, total, heads, n, mult);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+// out rows = rmsnorm(x rows; w, eps) * sigmoid(g rows) * mult; g may be null (no gate).  x float, w float [d].
+ZLM_EXPORT int zlm_norm_gate(const float* x, long x_stride, const float* w, const void* g, long g_stride, void* out,
+                             long out_stride, int dtype, int n_rows, int d, float eps, float mult, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (d <= 0) return ZLM_ERR_BAD_ARG;
+    const int threads = norm_threads(d);
+    cudaError_t e;
+    if (dtype == ZLM_F32)
+        e = launch_pdl(norm_gate_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, w, (const float*)g,
+                       g_stride, (float*)out, out_stride, d, eps, mult);
+    else if (dtype == ZLM_BF16)
+        e = launch_pdl(norm_gate_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, w,
+                       (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride, d, eps, mult);
     else
         return ZLM_ERR_UNSUPPORTED;
     return e == cudaSuccess ? launch_status() : (int)e;

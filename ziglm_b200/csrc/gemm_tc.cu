@@ -44,6 +44,12 @@ constexpr int A_BYTES = TC_BM * TC_BK * 2;
 
 enum OutMode { OUT_F32 = 0, OUT_F32_ACC = 1, OUT_BF16 = 2, OUT_BF16_GLU = 3, OUT_BF16_GEGLU = 4 };
 
+// The activations a plain bf16 product can apply to its float32 sums: 1 the squared relu, 2 the exact gelu.
+__device__ __forceinline__ float unary_activation(float v, int kind) {
+    if (kind == 1) { v = fmaxf(v, 0.f); return v * v; }
+    return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+}
+
 struct TcArgs {
     const void* bias;
     int bias_dtype;
@@ -59,7 +65,7 @@ struct TcArgs {
     int glu_kind;        // gated mode: 0 silu, 1 tanh gelu
     float glu_limit;     // gated mode, silu: > 0 makes it the clamped swish min(g, L) sigmoid(slope min(g, L)) (clamp(u, -L, L) + 1)
     float glu_slope;
-    int unary_act;       // plain bf16 output: 0 none, 1 the squared relu max(y, 0)^2 on every element before it is rounded
+    int unary_act;       // plain bf16 output: 0 none, 1 the squared relu max(y, 0)^2, 2 the exact gelu y (1 + erf(y / sqrt 2)) / 2, on every element before it is rounded
     // RMSNorm split over two products (steps of a few tokens, see zlm_gemm_tc_norm):
     // this product finishes the residual sum and leaves x * gain as bf16 and the sums of squares per tile row
     const void* norm_gain;      // [N] gain of the norm that follows, or null
@@ -181,7 +187,7 @@ __device__ __forceinline__ void store_tile(const TcArgs& a, const CUtensorMap* t
             float val = __uint_as_float(v[j]);
             if (a.scale_ssq != nullptr) val *= inv_s[(c * 16 + j) & 63];
             val += bias_v;
-            if (!GLU && a.unary_act == 1) { val = fmaxf(val, 0.f); val *= val; }
+            if (!GLU && a.unary_act) val = unary_activation(val, a.unary_act);
             if (GLU) {
                 // even lanes hold a gate row, the next lane the matching up row
                 const float up = __shfl_down_sync(0xffffffffu, val, 1);
@@ -436,7 +442,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                     for (int r = 1; r < 8; ++r) val += part[r];
                     if (a.scale_ssq != nullptr) val *= inv_s[cc];
                     val += bias_v;
-                    if (!GLU && a.unary_act == 1) { val = fmaxf(val, 0.f); val *= val; }
+                    if (!GLU && a.unary_act) val = unary_activation(val, a.unary_act);
                     if (GLU) {
                         const float up = __shfl_down_sync(0xffffffffu, val, 1);
                         const float g = val;
@@ -495,7 +501,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant
                         for (int r = 1; r < 8; ++r) v += part[u][r];     // in rank order
                         if (a.scale_ssq != nullptr) v *= inv_s[cc & 63];
                         v += bias_v;
-                        if (!GLU && a.unary_act == 1) { v = fmaxf(v, 0.f); v *= v; }
+                        if (!GLU && a.unary_act) v = unary_activation(v, a.unary_act);
                         if (GLU) {
                             const float up = __shfl_down_sync(0xffffffffu, v, 1);
                             const float g = v;
@@ -1115,10 +1121,10 @@ ZLM_EXPORT int zlm_gemm_tc_swish_clamped(const void* X, const void* W, const voi
                        nullptr, nullptr, nullptr, 0, 0.f, limit, slope, stream);
 }
 
-// Y = act(X W^T + bias) as bf16; unary 1: the squared relu.
+// Y = act(X W^T + bias) as bf16; unary 1: the squared relu, 2: the exact (erf) gelu.
 ZLM_EXPORT int zlm_gemm_tc_unary(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int T, int N,
                                  int K, long ldx, long ldw, long ldy, int unary, cudaStream_t stream) {
-    if (unary != 1) return ZLM_ERR_BAD_ARG;
+    if (unary != 1 && unary != 2) return ZLM_ERR_BAD_ARG;
     return gemm_tc_run(X, W, bias, bias_dtype, Y, ZLM_BF16, 0, 0, T, N, K, ldx, ldw, ldy, 0, nullptr, ZLM_F32, 0.f, nullptr, 0,
                        nullptr, nullptr, nullptr, 0, 0.f, 0.f, 1.f, stream, unary);
 }

@@ -1,0 +1,197 @@
+// Linear attention with a fixed decay per head, over a step's sequences, with the state carried in float:
+//     S_t = a S_(t-1) + k_t v_t^T          (S: [D, V] per sequence and head, zero at the start)
+//     o_t = S_t^T q_t
+// q, k, v are read from the rows of a projection (optionally through silu).  Unrolled over a chunk of n tokens
+// that starts behind the state S:
+//     o_i = sum_{j <= i} a^(i-j) (q_i . k_j) v_j  +  a^(i+1) S^T q_i
+//     S'  = a^n S + sum_j a^(n-1-j) k_j v_j^T
+// so a chunk is three small matrix products instead of n steps, and a prompt of thousands of tokens is
+// T/32 steps of a loop.  A decoded token is a chunk of one.  A block owns one (sequence, head, tile of 32 value
+// columns): the columns of S are independent of one another, so the tiles of a head need nothing from each other
+// but the scores q_i . k_j, which each computes for itself.  Every product is float FMA in a fixed order: the
+// scores and their weights, the state and the outputs never pass through a 16-bit type.
+#include "common.cuh"
+
+namespace zlm {
+
+constexpr int LA_C = 32;          // tokens of a chunk
+constexpr int LA_VT = 32;         // value columns of a block
+constexpr int LA_THREADS = 256;
+constexpr int LA_WARPS = LA_THREADS / 32;
+constexpr int LA_MAX_D = 512;
+
+__device__ __forceinline__ float la_act(float x, int act) { return act == 1 ? x / (1.0f + expf(-x)) : x; }
+
+// Shared memory, in floats, for a key size padded to Dp (a multiple of 4):
+//   q_s [C][Dp], kT_s [Dp][C+1], v_s [C][VT], a_s [C][C+1], S_s [Dp][VT]
+static inline size_t la_smem_floats(int Dp) {
+    return (size_t)LA_C * Dp + (size_t)Dp * (LA_C + 1) + (size_t)LA_C * LA_VT + (size_t)LA_C * (LA_C + 1) + (size_t)Dp * LA_VT;
+}
+
+// pows: float [H][C+1], pows[h][n] = decay_h^n.  state: float [slots][H][D][V].  out: float rows [T][H*V].
+template <typename T>
+__global__ void __launch_bounds__(LA_THREADS)
+decayed_linear_attention_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_off, int v_off, int H,
+                                int D, int Dp, int V, int act, const float* __restrict__ pows,
+                                float* __restrict__ state, const int* __restrict__ slots,
+                                const int* __restrict__ cu_seqlens, float* __restrict__ out, long out_stride) {
+    extern __shared__ __align__(16) float la_smem[];
+    float* q_s = la_smem;                              // [C][Dp]
+    float* kT_s = q_s + LA_C * Dp;                     // [Dp][C+1]
+    float* v_s = kT_s + Dp * (LA_C + 1);               // [C][VT]
+    float* a_s = v_s + LA_C * LA_VT;                   // [C][C+1]
+    float* S_s = a_s + LA_C * (LA_C + 1);              // [Dp][VT]
+    __shared__ float pw[LA_C + 1];
+
+    pdl_launch_dependents();
+    const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * LA_VT;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nv = min(LA_VT, V - v0);                 // value columns of this tile
+    for (int i = threadIdx.x; i <= LA_C; i += LA_THREADS) pw[i] = pows[h * (LA_C + 1) + i];
+    pdl_wait();
+    const int first = cu_seqlens[b], last = cu_seqlens[b + 1];
+    float* st = state + (((long)slots[b] * H + h) * D) * V;
+    for (int i = threadIdx.x; i < Dp * LA_VT; i += LA_THREADS) {
+        const int d = i / LA_VT, v = i % LA_VT;
+        S_s[i] = (d < D && v < nv) ? st[(long)d * V + v0 + v] : 0.f;
+    }
+
+    for (int c0 = first; c0 < last; c0 += LA_C) {
+        const int n = min(LA_C, last - c0);
+        __syncthreads();                               // the chunk before is done with q_s, kT_s, v_s, a_s
+        for (int i = threadIdx.x; i < LA_C * Dp; i += LA_THREADS) {
+            const int j = i / Dp, d = i % Dp;
+            float qv = 0.f, kv = 0.f;
+            if (j < n && d < D) {
+                const T* row = proj + (long)(c0 + j) * row_stride + (long)h * D + d;
+                qv = la_act(to_float(row[q_off]), act);
+                kv = la_act(to_float(row[k_off]), act);
+            }
+            q_s[j * Dp + d] = qv;
+            kT_s[d * (LA_C + 1) + j] = kv;
+        }
+        for (int i = threadIdx.x; i < LA_C * LA_VT; i += LA_THREADS) {
+            const int j = i / LA_VT, v = i % LA_VT;
+            v_s[i] = (j < n && v < nv) ? la_act(to_float(proj[(long)(c0 + j) * row_stride + v_off + (long)h * V + v0 + v]), act)
+                                       : 0.f;
+        }
+        __syncthreads();
+        // scores with their decay: a_s[i][j] = a^(i-j) (q_i . k_j) for j <= i.  A thread: rows warp, warp+8, .., column lane.
+        {
+            float s[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int d = 0; d < Dp; d += 4) {
+                const float k0 = kT_s[(d + 0) * (LA_C + 1) + lane], k1 = kT_s[(d + 1) * (LA_C + 1) + lane];
+                const float k2 = kT_s[(d + 2) * (LA_C + 1) + lane], k3 = kT_s[(d + 3) * (LA_C + 1) + lane];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const float4 qv = *reinterpret_cast<const float4*>(q_s + (warp + LA_WARPS * r) * Dp + d);
+                    s[r] = fmaf(qv.x, k0, s[r]); s[r] = fmaf(qv.y, k1, s[r]);
+                    s[r] = fmaf(qv.z, k2, s[r]); s[r] = fmaf(qv.w, k3, s[r]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int i = warp + LA_WARPS * r;
+                a_s[i * (LA_C + 1) + lane] = lane <= i ? s[r] * pw[i - lane] : 0.f;
+            }
+        }
+        __syncthreads();
+        // outputs: o_i = sum_j a_s[i][j] v_j + a^(i+1) S^T q_i.  A thread: rows warp, warp+8, .., value column lane.
+        {
+            float o[4] = {0.f, 0.f, 0.f, 0.f}, p[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < n; ++j) {
+                const float vv = v_s[j * LA_VT + lane];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) o[r] = fmaf(a_s[(warp + LA_WARPS * r) * (LA_C + 1) + j], vv, o[r]);
+            }
+            for (int d = 0; d < Dp; d += 4) {
+                const float s0 = S_s[(d + 0) * LA_VT + lane], s1 = S_s[(d + 1) * LA_VT + lane];
+                const float s2 = S_s[(d + 2) * LA_VT + lane], s3 = S_s[(d + 3) * LA_VT + lane];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const float4 qv = *reinterpret_cast<const float4*>(q_s + (warp + LA_WARPS * r) * Dp + d);
+                    p[r] = fmaf(qv.x, s0, p[r]); p[r] = fmaf(qv.y, s1, p[r]);
+                    p[r] = fmaf(qv.z, s2, p[r]); p[r] = fmaf(qv.w, s3, p[r]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int i = warp + LA_WARPS * r;
+                if (i < n && lane < nv)
+                    out[(long)(c0 + i) * out_stride + (long)h * V + v0 + lane] = fmaf(pw[i + 1], p[r], o[r]);
+            }
+        }
+        __syncthreads();                               // everyone has read the old state and v_s
+        // the values weighted for the state: v_j a^(n-1-j)
+        for (int i = threadIdx.x; i < LA_C * LA_VT; i += LA_THREADS) {
+            const int j = i / LA_VT;
+            if (j < n) v_s[i] *= pw[n - 1 - j];
+        }
+        __syncthreads();
+        // S' = a^n S + sum_j k_j (v_j a^(n-1-j))^T.  A thread: key dimensions warp, warp+8, .., value column lane.
+        {
+            const float an = pw[n];
+            for (int d0 = warp; d0 < Dp; d0 += LA_WARPS * 8) {
+                float acc[8];
+#pragma unroll
+                for (int r = 0; r < 8; ++r) acc[r] = 0.f;
+                for (int j = 0; j < n; ++j) {
+                    const float vv = v_s[j * LA_VT + lane];
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        const int d = d0 + LA_WARPS * r;
+                        if (d < Dp) acc[r] = fmaf(kT_s[d * (LA_C + 1) + j], vv, acc[r]);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    const int d = d0 + LA_WARPS * r;
+                    if (d < Dp) S_s[d * LA_VT + lane] = fmaf(an, S_s[d * LA_VT + lane], acc[r]);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < Dp * LA_VT; i += LA_THREADS) {
+        const int d = i / LA_VT, v = i % LA_VT;
+        if (d < D && v < nv) st[(long)d * V + v0 + v] = S_s[i];
+    }
+}
+
+}  // namespace zlm
+
+using namespace zlm;
+
+// The chunk length the table of powers must cover: pows is float [H][zlm_linear_attention_chunk() + 1].
+ZLM_EXPORT int zlm_linear_attention_chunk() { return LA_C; }
+
+// proj: rows [T][row_stride] of the step's type; head h's query lies at columns q_off + h*D, its key at k_off + h*D,
+// its value at v_off + h*V.  act 0: as they are, 1: through silu.  pows: float [H][chunk + 1] with decay_h^n.
+// state: float [n_slots][H][D][V]; slots, cu_seqlens: the step's sequences.  out: float rows [T][out_stride].
+ZLM_EXPORT int zlm_decayed_linear_attention(const void* proj, int dtype, long row_stride, int q_off, int k_off, int v_off,
+                                            int H, int D, int V, int act, const float* pows, float* state,
+                                            const int* slots, const int* cu_seqlens, int n_seqs, float* out,
+                                            long out_stride, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (H <= 0 || D <= 0 || V <= 0 || (act != 0 && act != 1)) return ZLM_ERR_BAD_ARG;
+    if (D > LA_MAX_D || H > 65535 || (V + LA_VT - 1) / LA_VT > 65535) return ZLM_ERR_UNSUPPORTED;
+    const int Dp = (D + 3) / 4 * 4;
+    const size_t smem = la_smem_floats(Dp) * sizeof(float);
+    dim3 grid(n_seqs, H, (V + LA_VT - 1) / LA_VT);
+    cudaError_t e;
+    if (dtype == ZLM_F32) {
+        auto kernel = decayed_linear_attention_kernel<float>;
+        if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
+            return (int)e;
+        e = launch_pdl(kernel, grid, dim3(LA_THREADS), smem, stream, (const float*)proj, row_stride, q_off, k_off, v_off, H,
+                       D, Dp, V, act, pows, state, slots, cu_seqlens, out, out_stride);
+    } else if (dtype == ZLM_BF16) {
+        auto kernel = decayed_linear_attention_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
+            return (int)e;
+        e = launch_pdl(kernel, grid, dim3(LA_THREADS), smem, stream, (const __nv_bfloat16*)proj, row_stride, q_off, k_off,
+                       v_off, H, D, Dp, V, act, pows, state, slots, cu_seqlens, out, out_stride);
+    } else
+        return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
+}

@@ -121,7 +121,7 @@ class Engine:
         spec = config.model_spec()
         declared = declare_parameters(spec)
         torch.cuda.set_device(device)
-        tensors = load_tensors(model_path, declared, dtype, device)
+        tensors = load_tensors(model_path, declared, dtype, device, tuple(spec.options.get("ignored_tensors", ())))
         model = Model(spec, dtype, device)
         model.bind(tensors)
         return cls(config, model, options)

@@ -62,6 +62,10 @@ _PROTOTYPES = {
         "zlm_unary_act": [c_void_p, c_void_p, c_int, c_long, c_int, c_void_p],
         "zlm_sigmoid_mul": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_void_p],
         "zlm_add_row": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "zlm_convert_rows": [c_void_p, c_int, c_long, c_void_p, c_int, c_long, c_int, c_int, c_void_p],
+        "zlm_gate_heads": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_float, c_void_p],
+        "zlm_norm_gate": [c_void_p, c_long, c_void_p, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_float,
+                          c_float, c_void_p],
         "zlm_scale": [c_void_p, c_long, c_float, c_void_p],
         "zlm_add": [c_void_p, c_void_p, c_long, c_void_p],
         "zlm_convert": [c_void_p, c_int, c_void_p, c_int, c_long, c_void_p],
@@ -76,6 +80,11 @@ _PROTOTYPES = {
                             c_void_p, c_int, c_int, c_int, c_void_p],
         "zlm_gated_scan": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_long, c_void_p, c_long, c_void_p, c_float,
                            c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    },
+    "linear_attention": {
+        "zlm_linear_attention_chunk": [],
+        "zlm_decayed_linear_attention": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                         c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_long, c_void_p],
     },
     "moe": {
         "zlm_moe_route": [c_void_p, c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -98,8 +107,11 @@ _PROTOTYPES = {
         "zlm_rope_norm_store": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_int,
                                 c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_void_p],
         "zlm_attention_general": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
-                                  c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_int,
-                                  c_void_p, c_long, c_void_p],
+                                  c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_long,
+                                  c_int, c_void_p, c_long, c_void_p],
+        "zlm_qk_prep": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                        c_int, c_float, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                        c_void_p, c_int, c_long, c_void_p],
         "zlm_attention_general_scratch": [c_int, c_int, c_int, c_int, c_int],
     },
     "attention_tc": {
@@ -317,11 +329,11 @@ def norm_add_scaled(branch: torch.Tensor, weight: torch.Tensor, eps: float, mult
         x.data_ptr(), _ptr(h), code(h.dtype) if h is not None else F32, n, d, _stream()), "norm_add_scaled")
 
 
-UNARY_ACTIVATIONS = {"relu2": 0}
+UNARY_ACTIVATIONS = {"relu2": 0, "gelu": 1}
 
 
 def unary_act(x: torch.Tensor, out: torch.Tensor, activation: str) -> None:
-    """out = act(x) element by element (out may be x); "relu2": max(x, 0)^2."""
+    """out = act(x) element by element (out may be x); "relu2": max(x, 0)^2, "gelu": x (1 + erf(x / sqrt 2)) / 2."""
     _cuda(x, "x"); _cuda(out, "out", x.dtype)
     if activation not in UNARY_ACTIVATIONS or out.shape != x.shape:
         raise KernelError(f"unary_act: activation {activation!r} is not known, or the shapes differ")
@@ -338,6 +350,48 @@ def sigmoid_mul(a: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
     _check(_fn("elementwise", "zlm_sigmoid_mul")(a.data_ptr(), _row_stride(a), gate.data_ptr(), _row_stride(gate),
                                                  out.data_ptr(), _row_stride(out), code(a.dtype), T, n, _stream()),
            "sigmoid_mul")
+
+
+def convert_rows(src: torch.Tensor, out: torch.Tensor) -> None:
+    """out = src, converted to out's type; both [T, n], each may be a column slice of a wider matrix."""
+    _rows(src, "src"); _rows(out, "out")
+    if src.shape != out.shape:
+        raise KernelError("convert_rows: the shapes differ")
+    _check(_fn("elementwise", "zlm_convert_rows")(src.data_ptr(), code(src.dtype), _row_stride(src), out.data_ptr(),
+                                                  code(out.dtype), _row_stride(out), src.shape[0], src.shape[1], _stream()),
+           "convert_rows")
+
+
+def gate_heads(a: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, n_heads: int, mult: float = 1.0) -> None:
+    """out[t, h, :] = a[t, h, :] * sigmoid(gate[t, h]) * mult: one gate a head.  a and out [T, n_heads * n], gate
+    [T, n_heads], all of one type; each may be a column slice of a wider matrix (out may be a)."""
+    _rows(a, "a"); _rows(gate, "gate"); _rows(out, "out")
+    T, width = a.shape
+    if (n_heads <= 0 or width % n_heads or gate.shape != (T, n_heads) or out.shape != a.shape or a.dtype != gate.dtype
+            or a.dtype != out.dtype):
+        raise KernelError("gate_heads: a and out must be [T, heads * n] and the gate [T, heads], of one type")
+    _check(_fn("elementwise", "zlm_gate_heads")(a.data_ptr(), _row_stride(a), gate.data_ptr(), _row_stride(gate),
+                                                out.data_ptr(), _row_stride(out), code(a.dtype), T, n_heads,
+                                                width // n_heads, float(mult), _stream()), "gate_heads")
+
+
+def norm_gate(x: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, eps: float,
+              mult: float = 1.0) -> None:
+    """out[r] = x[r] / sqrt(mean(x[r]^2) + eps) * weight * sigmoid(gate[r]) * mult (no gate: without the sigmoid).
+    x float32 rows, weight float32 [d], gate and out rows of one type; each may be a column slice."""
+    _rows(x, "x"); _rows(out, "out"); _cuda(weight, "weight", torch.float32)
+    n, d = x.shape
+    if x.dtype != torch.float32 or out.shape != (n, d) or weight.numel() != d:
+        raise KernelError("norm_gate: x must be float32, out of its shape, weight of its width")
+    g_stride = 0
+    if gate is not None:
+        _rows(gate, "gate")
+        if gate.shape != (n, d) or gate.dtype != out.dtype:
+            raise KernelError("norm_gate: the gate must have out's shape and type")
+        g_stride = _row_stride(gate)
+    _check(_fn("elementwise", "zlm_norm_gate")(x.data_ptr(), _row_stride(x), weight.data_ptr(), _ptr(gate), g_stride,
+                                               out.data_ptr(), _row_stride(out), code(out.dtype), n, d, float(eps),
+                                               float(mult), _stream()), "norm_gate")
 
 
 def add_row(x: torch.Tensor, row: torch.Tensor) -> None:
@@ -675,6 +729,82 @@ def rope_norm_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, r
         "rope_norm_store")
 
 
+def qk_prep(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, rotary_dim: int,
+            inv_freq: Optional[torch.Tensor], q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+            q_count: int, k_count: int, norm_eps: float, mix_mode: int, mix: float, mix_buf: Optional[torch.Tensor],
+            value_dim: int, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+            k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], page_size: int) -> None:
+    """What stands between the q|k|v product and attention when q and k are normed as whole vectors, in one kernel:
+    rows [q heads | k heads | v heads | ...] of ``qkv`` are changed in place and k, v stored in the cache pages.
+
+    ``q_weight`` / ``k_weight`` (float32, laid out like the q / k heads of a row; None: not normed): q and k, each as
+    one vector, are divided by sqrt(mean square + norm_eps), the mean taken over ``q_count`` / ``k_count`` elements (heads
+    kept with zeros behind them have fewer true elements), and multiplied by the weight; then the first ``rotary_dim``
+    dimensions of every head are turned (pairs i, i + rotary_dim/2).  ``mix_mode`` 1: the values (the first ``value_dim``
+    elements of every value head; the rest is zeros the head is kept with) are also left in ``mix_buf``
+    [T, n_kv * value_dim]; 2: v <- (1 - mix) v + mix * mix_buf."""
+    _rows(qkv, "qkv"); _cuda(positions, "positions", torch.int32); _cuda(seq_of_token, "seq_of_token", torch.int32)
+    _cuda(block_table, "block_table", torch.int32)
+    T = qkv.shape[0]
+    if qkv.shape[1] < (n_heads + 2 * n_kv) * head_dim:
+        raise KernelError("qk_prep: the rows are narrower than the heads")
+    if inv_freq is not None:
+        _cuda(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() * 2 != rotary_dim:
+            raise KernelError("qk_prep: the frequency table must hold rotary_dim/2 entries")
+    for w, n in ((q_weight, n_heads), (k_weight, n_kv)):
+        if w is not None:
+            _cuda(w, "norm weight", torch.float32)
+            if w.numel() != n * head_dim:
+                raise KernelError("qk_prep: a norm weight must be laid out like its heads")
+    if mix_mode:
+        _cuda(mix_buf, "mix_buf", qkv.dtype)
+        if mix_buf.shape != (T, n_kv * value_dim) or not mix_buf.is_contiguous():
+            raise KernelError("qk_prep: the buffer of mixed values must be [T, n_kv * value_dim]")
+    page_stride = 0
+    if k_pages is not None:
+        _cuda(k_pages, "k_pages", qkv.dtype); _cuda(v_pages, "v_pages", qkv.dtype)
+        if tuple(k_pages.shape[1:]) != (n_kv, page_size, head_dim) or k_pages.shape != v_pages.shape:
+            raise KernelError("qk_prep: cache pages must be [n_pages, n_kv, page_size, head_dim]")
+        page_stride = k_pages.stride(0)
+    _check(_fn("attention", "zlm_qk_prep")(
+        qkv.data_ptr(), code(qkv.dtype), _row_stride(qkv), T, n_heads, n_kv, head_dim, rotary_dim, _ptr(inv_freq),
+        _ptr(q_weight), _ptr(k_weight), int(q_count), int(k_count), float(norm_eps), int(mix_mode), float(mix),
+        _ptr(mix_buf) if mix_mode else None, int(value_dim), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), _ptr(k_pages), _ptr(v_pages), page_size, page_stride, _stream()), "qk_prep")
+
+
+def linear_attention_chunk() -> int:
+    """Tokens of a chunk of ``decayed_linear_attention``: the table of decay powers holds this many plus one a head."""
+    return int(_fn("linear_attention", "zlm_linear_attention_chunk")())
+
+
+def decayed_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n_heads: int, dim: int,
+                             value_dim: int, activation: Optional[str], pows: torch.Tensor, state: torch.Tensor, step,
+                             out: torch.Tensor) -> None:
+    """Linear attention with a fixed decay per head over the step's sequences: per head S <- a S + k v^T (float32
+    [dim, value_dim], carried in ``state`` [slots, n_heads, dim, value_dim]) and o = S^T q.  Head h's q, k, v are the
+    columns q_off + h*dim, k_off + h*dim, v_off + h*value_dim of ``proj``'s rows, read through ``activation``
+    (None or "silu").  ``pows`` float32 [n_heads, chunk + 1]: decay_h^n.  ``out`` float32 [T, n_heads * value_dim]."""
+    _rows(proj, "proj"); _rows(out, "out"); _cuda(pows, "pows", torch.float32); _cuda(state, "state", torch.float32)
+    T = proj.shape[0]
+    if activation not in (None, "silu"):
+        raise KernelError(f"decayed_linear_attention: activation {activation!r} is not known (silu)")
+    if out.dtype != torch.float32 or out.shape != (T, n_heads * value_dim):
+        raise KernelError("decayed_linear_attention: out must be float32 [T, heads * value_dim]")
+    if (max(q_off, k_off) + n_heads * dim > proj.shape[1] or v_off + n_heads * value_dim > proj.shape[1]
+            or min(q_off, k_off, v_off) < 0):
+        raise KernelError("decayed_linear_attention: the heads lie outside the rows")
+    if tuple(state.shape[1:]) != (n_heads, dim, value_dim) or not state.is_contiguous():
+        raise KernelError("decayed_linear_attention: the state must be [slots, heads, dim, value_dim]")
+    if tuple(pows.shape) != (n_heads, linear_attention_chunk() + 1) or not pows.is_contiguous():
+        raise KernelError("decayed_linear_attention: the table of powers must be [heads, chunk + 1]")
+    _check(_fn("linear_attention", "zlm_decayed_linear_attention")(
+        proj.data_ptr(), code(proj.dtype), _row_stride(proj), q_off, k_off, v_off, n_heads, dim, value_dim,
+        1 if activation == "silu" else 0, pows.data_ptr(), state.data_ptr(), step.slots.data_ptr(),
+        step.cu_seqlens.data_ptr(), step.n_seqs, out.data_ptr(), _row_stride(out), _stream()), "decayed_linear_attention")
+
+
 def attention_general_scratch(n_tokens: int, n_heads: int, n_kv: int, head_dim: int, max_keys: int) -> int:
     """Floats of scratch with which ``attention_general`` spreads a step of few tokens over more blocks (0: none
     is of use)."""
@@ -685,9 +815,11 @@ def attention_general(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: 
                       window: Optional[int], positions: torch.Tensor, seq_of_token: torch.Tensor,
                       block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       page_size: int, max_keys: int = 0, scratch: Optional[torch.Tensor] = None,
-                      softcap: float = 0.0) -> None:
+                      softcap: float = 0.0, keep_first: int = 0, sinks: Optional[torch.Tensor] = None) -> None:
     """out[t, h, :] = softmax(q[t,h] . K[start..pos_t] * scale) @ V over the paged cache; with ``softcap`` c > 0 the
-    scaled scores become c * tanh(score / c) before the softmax.
+    scaled scores become c * tanh(score / c) before the softmax.  With a window, the first ``keep_first`` positions
+    of a sequence stay visible behind it.  ``sinks`` (float32, one per query head): exp(sinks[h]) is added to the
+    softmax's denominator; it has no key and no value and is not scaled.
 
     The queries are the first n_heads*head_dim columns of each row of ``qkv`` (any row stride).
     ``max_keys`` (the most keys a token of the step sees) and ``scratch`` (float32, at least
@@ -706,9 +838,13 @@ def attention_general(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: 
         raise KernelError(f"attention: head size {head_dim} is not supported (a multiple of 8, at most 512)")
     if tuple(k_pages.shape[1:]) != (n_kv, page_size, head_dim) or k_pages.shape != v_pages.shape:
         raise KernelError("attention: cache pages must be [n_pages, n_kv, page_size, head_dim]")
+    if sinks is not None:
+        _cuda(sinks, "sinks", torch.float32)
+        if sinks.numel() != n_heads:
+            raise KernelError("attention: one sink per query head is needed")
     _check(_fn("attention", "zlm_attention_general")(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), code(qkv.dtype), T, n_heads, n_kv, head_dim, scale,
-        float(softcap or 0.0), int(window or 0), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
+        float(softcap or 0.0), int(window or 0), int(keep_first or 0), _ptr(sinks), positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), page_size, k_pages.stride(0), int(max_keys),
         _ptr(scratch), scratch.numel() if scratch is not None else 0, _stream()),
         "attention_general")
@@ -947,13 +1083,18 @@ def attention_with_rope(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int
 
 
 def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
-              window: Optional[int], io, softcap: float = 0.0, gate: Optional[torch.Tensor] = None) -> bool:
+              window: Optional[int], io, softcap: float = 0.0, gate: Optional[torch.Tensor] = None,
+              keep_first: int = 0, sinks: Optional[torch.Tensor] = None) -> bool:
     """Attention of a step's tokens over the cache of the running layer; picks the kernel.  ``softcap`` c > 0:
-    the scaled scores become c * tanh(score / c).  ``gate`` ([T, n_heads * head_dim] of the step's type): the flat
+    the scaled scores become c * tanh(score / c).  ``keep_first``: with a window, the first positions of a sequence
+    that stay visible behind it.  ``sinks`` (float32, one per query head): a number in the softmax's denominator that
+    belongs to no key.  ``gate`` ([T, n_heads * head_dim] of the step's type): the flat
     decode kernel multiplies its output by sigmoid(gate) before rounding it; the result says whether that was done
     (the caller multiplies when it was not: in a prompt one pass of ``sigmoid_mul`` over coalesced rows costs less
     than the same work in the prompt kernel's epilogue, where every thread walks a row of its own)."""
-    if _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
+    keep_first = int(keep_first or 0) if window else 0
+    plain_only = keep_first > 0 or sinks is not None      # the tensor-core kernels know neither
+    if not plain_only and _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
         n_blocks = attention_decode_flat_blocks(step.n_tokens, n_heads, n_kv, head_dim) if step.single_token else 0
         if n_blocks > 0:
             need = attention_decode_flat_scratch(step.n_tokens, n_heads, n_kv, head_dim, n_blocks)
@@ -979,16 +1120,21 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
                 return False
             if attention_prefill(*args, softcap=softcap):
                 return False
-    max_keys = min(step.max_total, window) if window else step.max_total
+    max_keys = min(step.max_total, window + keep_first) if window else step.max_total
     need = attention_general_scratch(step.n_tokens, n_heads, n_kv, head_dim, max_keys)
     scratch = step.ws.buf("attn_parts", (need,), torch.float32) if need > 0 else None
     attention_general(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions, step.seq_of_token,
-                      io.block_table, io.k_pages, io.v_pages, io.page_size, max_keys, scratch, softcap=softcap)
+                      io.block_table, io.k_pages, io.v_pages, io.page_size, max_keys, scratch, softcap=softcap,
+                      keep_first=keep_first, sinks=sinks)
     return False
 
 
-def fast_attention_libraries(dtype: torch.dtype, head_dim: int, n_heads: int = 1, n_kv: int = 1, softcap: float = 0.0):
-    """The sources of the tensor-core attention kernels if they take this shape, else nothing (the plain kernel runs)."""
+def fast_attention_libraries(dtype: torch.dtype, head_dim: int, n_heads: int = 1, n_kv: int = 1, softcap: float = 0.0,
+                             keep_first: int = 0, sinks: bool = False):
+    """The sources of the tensor-core attention kernels if they take this shape and these options, else nothing (the
+    plain kernel runs)."""
+    if keep_first or sinks:
+        return ()
     return ("attention_tc", "attention_fmha") if _tc_attention_ok(dtype, n_heads, n_kv, head_dim, 64) else ()
 
 
@@ -1093,12 +1239,12 @@ def gemm_tc_swish_clamped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, l
 def gemm_tc_unary(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activation: str,
                   bias: Optional[torch.Tensor] = None) -> bool:
     """out [T, N] (bf16) = act(x w^T + bias) on the tensor cores, the activation applied to the float32 sums in the
-    epilogue ("relu2": max(y, 0)^2).  False, having done nothing, if the operands are not what TMA can read."""
+    epilogue ("relu2": max(y, 0)^2; "gelu": the exact, erf form).  False, having done nothing, if the operands are not what TMA can read."""
     _rows(x, "x"); _rows(w, "w"); _rows(out, "out")
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("gemm_tc_unary: x, w and out must be bfloat16")
-    if activation != "relu2":
-        raise KernelError(f"gemm_tc_unary: activation {activation!r} is not known (relu2)")
+    if activation not in UNARY_ACTIVATIONS:
+        raise KernelError(f"gemm_tc_unary: activation {activation!r} is not known ({', '.join(UNARY_ACTIVATIONS)})")
     T, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K or out.shape != (T, N):
@@ -1109,7 +1255,7 @@ def gemm_tc_unary(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, activatio
             raise KernelError("gemm_tc_unary: bias length does not match")
     status = _fn("gemm_tc", "zlm_gemm_tc_unary")(
         x.data_ptr(), w.data_ptr(), _ptr(bias), code(bias.dtype) if bias is not None else F32, out.data_ptr(), T, N, K,
-        _row_stride(x), _row_stride(w), _row_stride(out), 1, _stream())
+        _row_stride(x), _row_stride(w), _row_stride(out), UNARY_ACTIVATIONS[activation] + 1, _stream())
     if status == -2:
         return False
     _check(status, "gemm_tc_unary")

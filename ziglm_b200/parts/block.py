@@ -287,3 +287,69 @@ class PostNormBlock(Part):
 
 
 register_block("postnorm", PostNormBlock)
+
+
+class SharedNormBlock(Part):
+    """One norm whose rows the mixer and the feed-forward both read: with h = norm(x), x += mixer(h) + ff(h).
+
+    The two sublayers add into the float32 residual one after the other; neither reads what the other wrote, so the
+    sum is the arrangement's.  A layer whose spec has no feed-forward ends after the mixer.  ``spec.ffn_norm`` is not
+    used (it is None)."""
+
+    def __init__(self, spec: LayerSpec, dtype: torch.dtype, device: torch.device):
+        super().__init__(spec, dtype, device)
+        if spec.mixer_norm is None:
+            raise ValueError("shared_norm: the arrangement needs the norm both sublayers read")
+        self.parts: Dict[str, Part] = {}
+        for prefix, klass, sub in self._children(spec):
+            self.parts[prefix] = klass(sub, dtype, device)
+        self.mixer_norm = self.parts["mixer_norm."]
+        self.mixer = self.parts["mixer."]
+        self.ffn = self.parts.get("ffn.")
+
+    @classmethod
+    def _children(cls, spec: LayerSpec):
+        out = [("mixer_norm.", norm_class(spec.mixer_norm.kind), spec.mixer_norm),
+               ("mixer.", mixer_class(spec.mixer.kind), spec.mixer)]
+        if spec.ffn is not None:
+            out.append(("ffn.", feed_forward_class(spec.ffn.kind), spec.ffn))
+        return out
+
+    @classmethod
+    def declare(cls, spec: LayerSpec) -> Dict[str, ParamDecl]:
+        out: Dict[str, ParamDecl] = {}
+        for prefix, klass, sub in cls._children(spec):
+            for name, decl in klass.declare(sub).items():
+                out[prefix + name] = decl
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for prefix, part in self.parts.items():
+            part.bind({k[len(prefix):]: v for k, v in tensors.items() if k.startswith(prefix)})
+
+    def kernel_libraries(self) -> Tuple[str, ...]:
+        libs: Tuple[str, ...] = ()
+        for part in self.parts.values():
+            libs += part.kernel_libraries()
+        return libs
+
+    def cache_needs(self) -> Optional[KVNeed]:
+        return self.mixer.cache_needs()
+
+    def state_needs(self) -> Optional[StateNeed]:
+        return self.mixer.state_needs()
+
+    def accepts_normed_input(self) -> bool:
+        """The block before may hand this block's norm over as finished rows (``h_in``); a norm half done by a
+        product is not taken, since two sublayers would have to complete it."""
+        return False
+
+    def forward(self, step, io: LayerIO, x: torch.Tensor, h_in=None, next_norm=None):
+        h = h_in if isinstance(h_in, torch.Tensor) else self.mixer_norm.forward(step, x)
+        self.mixer.forward(step, io, h, x)
+        if self.ffn is not None:
+            self.ffn.forward(step, h, x)
+        return None
+
+
+register_block("shared_norm", SharedNormBlock)

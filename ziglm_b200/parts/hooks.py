@@ -4,6 +4,9 @@
               stream at a fixed place (the start of a pass through a repeated run of layers).  Options:
               ``rows`` and ``width`` (the table's shape), ``row``.
 ``scale``     logits *= factor.  Option: ``factor``.
+``rmsnorm``   x <- x / sqrt(mean(x^2) + eps) * (w + offset) over every row, in place and in float32: a norm of the
+              embedded tokens before the first layer.  Options: ``width``, ``eps``, ``unit_offset`` (the stored weight
+              is the gain minus one).
 """
 from __future__ import annotations
 
@@ -50,5 +53,31 @@ class Scale(Part):
         kernels.scale_(x, self.factor)
 
 
+class NormRows(Part):
+    def __init__(self, spec: HookSpec, dtype: torch.dtype, device: torch.device):
+        super().__init__(spec, dtype, device)
+        self.width = int(spec.options["width"])
+        self.eps = float(spec.options["eps"])
+        self.weight_offset = 1.0 if spec.options.get("unit_offset") else 0.0
+        self.weight: Optional[torch.Tensor] = None
+
+    @classmethod
+    def declare(cls, spec: HookSpec) -> Dict[str, ParamDecl]:
+        return {"weight": ParamDecl((int(spec.options["width"]),), init="zeros" if spec.options.get("unit_offset") else "ones")}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors["weight"].contiguous()
+
+    def kernel_libraries(self) -> Tuple[str, ...]:
+        return ("elementwise",)
+
+    def forward(self, step, x: torch.Tensor) -> None:
+        if x.shape[-1] != self.width:
+            raise ValueError(f"rmsnorm hook: rows of {x.shape[-1]} elements, the norm is over {self.width}")
+        # every element is read and written by the same thread, after the row's sum is known: in place is safe
+        kernels.rmsnorm_rows(x, self.weight, x, self.eps, weight_offset=self.weight_offset)
+
+
 register_hook("add_row", AddRow)
+register_hook("rmsnorm", NormRows)
 register_hook("scale", Scale)

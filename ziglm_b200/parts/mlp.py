@@ -105,7 +105,8 @@ register_feed_forward("gated_mlp", GatedMLP)
 
 
 class PlainMLP(Part):
-    """A feed-forward without a gate: down(act(up(x))).  ``activation``: "relu2", the squared relu max(z, 0)^2."""
+    """A feed-forward without a gate: down(act(up(x))).  ``activation``: "relu2", the squared relu max(z, 0)^2, or "gelu", the exact form
+    z (1 + erf(z / sqrt 2)) / 2."""
     can_overwrite = True
 
     def __init__(self, spec: FeedForwardSpec, dtype: torch.dtype, device: torch.device):

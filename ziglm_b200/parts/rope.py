@@ -28,6 +28,12 @@ so pairs that turn fast keep their frequency and slow ones are interpolated.  Th
 rotated queries and keys by ``attention_factor`` (default 0.1 ln(factor) + 1); since the whole head is
 rotated, that is the same as multiplying the scores by its square, which is what ``score_scale`` reports
 to the mixer.
+
+Which dimensions form a pair is a parameter (``pairs`` in the options of the spec): "halves", (i, i + rotary_dim/2),
+or "adjacent", (2i, 2i + 1).  The kernels turn halves.  A score q . k does not change when q and k are reordered
+alike, so a mixer whose pairs are adjacent reorders the rows of its q and k projections once, when the weights are
+bound, by ``Rope.head_order``: the even dimensions of the rotated part first, then the odd ones, then the rest;
+after that the halves are the pairs.
 """
 from __future__ import annotations
 
@@ -115,6 +121,20 @@ class Rope(Part):
         # or only a part of the head is rotated
         self.in_table = bool(spec.options.get("amplitude_in_table"))
         self.amplitude = self.factor if self.in_table else 1.0
+        self.pairs = spec.options.get("pairs", "halves")
+        if self.pairs not in ("halves", "adjacent"):
+            raise ValueError(f"rope: pairs {self.pairs!r} is not known (halves, adjacent)")
+
+    def head_order(self, head_dim: int) -> Optional[Tuple[int, ...]]:
+        """The order in which a mixer lays out the dimensions of every q and k head so that the pairs of this
+        encoding become the halves the kernels turn: element r of the result is the dimension that goes to place
+        r.  None: the pairs are the halves already."""
+        if self.pairs == "halves":
+            return None
+        R = self.rotary_dim
+        if R > head_dim:
+            raise ValueError(f"rope: {R} rotated dimensions in a head of {head_dim}")
+        return tuple(range(0, R, 2)) + tuple(range(1, R, 2)) + tuple(range(R, head_dim))
 
     def score_scale(self, head_dim: int) -> float:
         """What the mixer multiplies its scores by on behalf of this encoding."""
@@ -142,6 +162,9 @@ class NoPosition(Part):
         return 1.0
 
     def apply(self, step, qkv: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int) -> None:
+        return None
+
+    def head_order(self, head_dim: int):
         return None
 
 

@@ -56,11 +56,13 @@ def storage_dtype(stored: str, kind: str, run_dtype: torch.dtype) -> torch.dtype
 
 
 def check_against(folder: str, declared: Mapping[str, ParamDecl],
-                  found: Mapping[str, Tuple[str, Tuple[int, ...]]]) -> None:
-    """Raise one WeightError listing every disagreement between ``declared`` and ``found``."""
+                  found: Mapping[str, Tuple[str, Tuple[int, ...]]], ignored: Tuple[str, ...] = ()) -> None:
+    """Raise one WeightError listing every disagreement between ``declared`` and ``found``.  ``ignored``: patterns of
+    names a file may hold although the model does not use them (a design that writes a tensor for every layer of a
+    kind, also where an option that would read it is off)."""
     missing = [n for n in declared if n not in found]
     unexpected = [n for n in found if n not in declared
-                  and not any(fnmatch.fnmatch(n, pat) for pat in IGNORED_TENSORS)]
+                  and not any(fnmatch.fnmatch(n, pat) for pat in IGNORED_TENSORS + tuple(ignored))]
     wrong = []
     for n, decl in declared.items():
         if n not in found:
@@ -77,11 +79,11 @@ def check_against(folder: str, declared: Mapping[str, ParamDecl],
 
 
 def load_tensors(folder: str, declared: Mapping[str, ParamDecl], run_dtype: torch.dtype,
-                 device: torch.device) -> Dict[str, torch.Tensor]:
+                 device: torch.device, ignored: Tuple[str, ...] = ()) -> Dict[str, torch.Tensor]:
     """Read, check and move to ``device`` every declared tensor of ``folder``."""
     files, where = open_model_files(folder)
     found = {name: files[fname].info(name) for name, fname in where.items()}
-    check_against(folder, declared, found)
+    check_against(folder, declared, found, ignored)
     out: Dict[str, torch.Tensor] = {}
     for name, decl in declared.items():
         stored, _ = found[name]
