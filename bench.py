@@ -10,6 +10,7 @@
     python bench.py --case reference-kernels [--context C]     the reference's CUDA kernels alone, if they were built
     python bench.py --case tumatar [--shape 1b|8b] [--layers L]    the Tumatar design beside Llama at equal width, its kernels alone
     python bench.py --case tikalix [--shape 1b|8b] [--layers L]    the Tikalix design beside Llama at equal width, its kernels alone
+    python bench.py --case vilazen [--shape 1b|8b] [--layers L]    the Vilazen design beside Llama at equal width, its kernels alone
 
 A "step" is one decode step of a batch of 8 sequences at a context of 4096
 tokens.  ``value`` is decoded tokens a second, timed on the device with CUDA
@@ -715,6 +716,159 @@ def run_tikalix(args):
     return 0
 
 
+def run_vilazen(args):
+    """The Vilazen design beside the Llama shape of the same width and heads, with random weights: a prompt of
+    ``--prompt-tokens`` and decode steps of ``--batch`` sequences at ``--context``, ``--layers`` layers of each
+    (default 4: one of every kind and the value-mixing pair), and every kernel the design adds or changes, alone,
+    against its own roofline (the larger of bytes / measured copy bandwidth and FLOPs / measured bf16 peak; float32
+    FMA work against 2 x 128 lanes x 148 SMs x the clock), each beside the library's like kernel timed in the same run
+    on operands of the same size."""
+    import torch
+    from types import SimpleNamespace
+    from ziglm_b200 import kernels
+    from ziglm_b200.config.shapes import shape
+    from ziglm_b200.engine.workspace import Workspace
+    from ziglm_b200.parts.base import LayerIO
+    torch.cuda.set_device(0)
+    pk = peaks()
+    size = "8b" if args.shape == "8b" else "1b"
+    layers = args.layers or 4
+    T, batch, context = args.prompt_tokens, args.batch, args.context
+    max_seq = max(context, T) + 64
+    gen = torch.Generator().manual_seed(7)
+    out = {"case": "vilazen", "width_of": "llama-" + size, "dtype": "bf16", "layers": layers, "prompt_tokens": T,
+           "batch": batch, "context": context, "data": "synthetic", "l2": "a 256 MiB buffer is rewritten before every timed call",
+           "peaks": pk["source"], "models": {}}
+    for name in ("vilazen-" + size, "llama-" + size):
+        cfg = shape(name)
+        if "layers" in cfg:
+            cfg["layers"] = cfg["layers"][:layers]
+            vocab = cfg["vocab"]
+        else:
+            cfg["num_hidden_layers"] = layers
+            cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], max_seq)
+            vocab = cfg["vocab_size"]
+        eng = _engine_for(cfg, "bfloat16", batch, max_seq)
+        ids = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+        pre = _time_prompt(eng, ids(T), args.warmup, args.steps)
+        dec = _time_decode_at(eng, batch, context, args.warmup, args.steps, ids)
+        out["models"][name] = {"prefill_ms": round(pre, 3), "prefill_tok_s": round(T / pre * 1e3, 1),
+                               "decode_ms": round(dec, 4), "decode_tok_s": round(batch / dec * 1e3, 1)}
+        del eng
+        torch.cuda.empty_cache()
+    # ---- the kernels, alone
+    cfg = shape("vilazen-" + size)
+    d = cfg["width"]
+    par, att = cfg["layers"][0]["mixer"], cfg["layers"][1]["mixer"]
+    lin = par["right"]
+    ff = cfg["layers"][0]["mlp"]["ff"]
+    H, G, hd, scale = att["heads"], att["kv_heads"], att["dim"], att["scale"]
+    rot, window, keep = att["rot"]["dims"], att["mask"]["size"], att["mask"]["keep_first"]
+    LH, LD, LV = lin["heads"], lin["dim"], lin["vdim"]
+    dev = torch.device("cuda:0")
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    bf = lambda *sh: (torch.randn(*sh, device=dev) * 0.05).to(torch.bfloat16)
+    f32 = lambda *sh: torch.randn(*sh, device=dev) * 0.05
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    hbm, peak = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    fma = 2.0 * 128 * 148 * 1.9e9
+    rows = []
+
+    def report(what, like, ms, nbytes, flops, fma_flops=0.0):
+        floor = max(nbytes / hbm, flops / peak, fma_flops / fma) * 1e3
+        rows.append({"kernel": what, "like": like, "ms": round(ms, 4), "roofline_ms": round(floor, 4),
+                     "frac_of_roofline": round(floor / ms, 4)})
+
+    def timed(fn):
+        return _timed(fn, args.warmup, args.steps, flush)
+
+    kernels.require(("elementwise", "attention", "attention_tc", "attention_fmha", "linear_attention", "gemm_generic", "gemm_tc"))
+    page = 64
+    inv_freq = torch.rand(rot // 2, device=dev)
+    sinks = f32(H) * 20
+    chunk = kernels.linear_attention_chunk()
+    pows = torch.tensor([[a ** n for n in range(chunk + 1)] for a in lin["decay"]], dtype=torch.float64).float().to(dev)
+    for n_tok, tag in ((T, f"prompt of {T}"), (batch, f"decode batch {batch}")):
+        decode = n_tok != T
+        past = context - 1 if decode else 0
+        n_seq = n_tok if decode else 1
+        per_seq = -(-(past + (1 if decode else T)) // page)
+        k_pages, v_pages = bf(n_seq * per_seq, G, page, hd), bf(n_seq * per_seq, G, page, hd)
+        table = torch.arange(n_seq * per_seq, dtype=torch.int32, device=dev).view(n_seq, per_seq)
+        new = [1] * n_seq if decode else [T]
+        cu = [0]
+        for n in new:
+            cu.append(cu[-1] + n)
+        step = SimpleNamespace(
+            n_tokens=n_tok, n_seqs=n_seq, single_token=decode, max_new=max(new), max_total=past + max(new),
+            positions=i32([past + i for n in new for i in range(n)]), seq_of_token=i32([b for b, n in enumerate(new) for _ in range(n)]),
+            cu_seqlens=i32(cu), past_lens=i32([past] * n_seq), total_lens=i32([past + n for n in new]),
+            slots=i32(list(range(n_seq))), ws=Workspace(dev))
+        io = LayerIO(k_pages=k_pages, v_pages=v_pages, block_table=table, page_size=page)
+        # norm of the whole q and k + rotation + mixed values + cache write, beside the library's rotation + cache write
+        gcols = -(-H // 8) * 8
+        proj = bf(n_tok, (H + 2 * G) * hd + gcols)
+        qkv = bf(n_tok, (H + 2 * G) * hd)
+        wq, wk = f32(H * hd) + 1, f32(G * hd) + 1
+        mixb = bf(n_tok, G * hd)
+        rope_bytes = n_tok * (H + G) * hd * 4 + n_tok * G * hd * 2 * 3
+        ms = timed(lambda: kernels.rope_store(qkv, H, G, hd, rot, inv_freq, step.positions, step.seq_of_token, table, k_pages,
+                                              v_pages, page))
+        report(f"rope_store (rotation + cache write), {tag}", "-", ms, rope_bytes, 0)
+        ms = timed(lambda: kernels.qk_prep(proj, H, G, hd, rot, inv_freq, wq, wk, H * hd, G * hd, 1e-6, 2, 0.25, mixb, hd,
+                                           step.positions, step.seq_of_token, table, k_pages, v_pages, page))
+        report(f"qk_prep (norm of whole q and k + rotation + mixed values + cache write), {tag}", "rope_store", ms,
+               rope_bytes + n_tok * G * hd * 2 + (H + G) * hd * 4, 0)
+        # attention: a window, a window that keeps the first tokens; all keys, all keys with a number in the denominator
+        att_out = torch.empty(n_tok, H * hd, dtype=torch.bfloat16, device=dev)
+        for w, kf, sk, what, like in ((window, 0, None, f"attention, window {window}", "-"),
+                                      (window, keep, None, f"attention, window {window} keeping the first {keep}", f"attention, window {window}"),
+                                      (None, 0, None, "attention, every key", "-"),
+                                      (None, 0, sinks, "attention, every key, with sinks", "attention, every key")):
+            seen = lambda i: min(i + 1, (w + kf) if w else i + 1)
+            if decode:
+                keys = seen(past)
+                att_bytes, att_flops = n_seq * keys * G * hd * 2 * 2 + n_tok * H * hd * 4, 4.0 * n_tok * H * hd * keys
+            else:
+                pairs = sum(seen(i) for i in range(T))
+                att_bytes, att_flops = n_tok * (H + 2 * G) * hd * 2 + n_tok * H * hd * 2, 4.0 * H * hd * pairs
+            ms = timed(lambda: kernels.attention(step, qkv, att_out, H, G, hd, scale, w, io, keep_first=kf, sinks=sk))
+            report(f"{what}, {tag}", like, ms, att_bytes, att_flops)
+        ms = timed(lambda: kernels.sigmoid_mul(att_out, qkv[:, :H * hd], att_out))
+        report(f"sigmoid_mul (a gate an element), {tag}", "-", ms, n_tok * H * hd * 6, 0)
+        ms = timed(lambda: kernels.gate_heads(att_out, proj[:, (H + 2 * G) * hd:(H + 2 * G) * hd + H], att_out, H, 1.2))
+        report(f"gate_heads (a gate a head), {tag}", "sigmoid_mul", ms, n_tok * H * (hd * 4 + 2), 0)
+        # linear attention with a decay, beside attention over every key with as many heads of that size
+        lproj = bf(n_tok, LH * (2 * LD + 2 * LV))
+        state = torch.zeros(n_seq, LH, LD, LV, device=dev)
+        mixed = torch.empty(n_tok, LH * LV, device=dev)
+        la_bytes = n_tok * LH * (2 * LD + LV) * 2 + n_tok * LH * LV * 4 + n_seq * LH * LD * LV * 8
+        c = min(chunk, max(new))
+        la_fma = 2.0 * n_tok * LH * (c * LD + c * LV + 2 * LD * LV)
+        ms = timed(lambda: kernels.decayed_linear_attention(lproj, 0, LH * LD, 2 * LH * LD, LH, LD, LV, "silu", pows, state,
+                                                            step, mixed))
+        report(f"decayed_linear_attention ({LH} heads of {LD}), {tag}", "attention, every key", ms, la_bytes, 0, la_fma)
+        xr, wn, yn = f32(n_tok, d), bf(d), torch.empty(n_tok, d, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: kernels.rmsnorm(xr, wn, yn, 1e-6))
+        report(f"rmsnorm, {tag}", "-", ms, n_tok * d * 6 + d * 2, 0)
+        lout = torch.empty(n_tok, LH * LV, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: kernels.norm_gate(mixed, wq[:LH * LV].contiguous(), lproj[:, LH * (2 * LD + LV):], lout, 1e-6, 1.1))
+        report(f"norm_gate (norm of the heads + gate), {tag}", "rmsnorm", ms, n_tok * LH * LV * 8 + LH * LV * 4, 0)
+        # the feed-forward's first product with the exact gelu, beside the gated product of as many rows
+        x, wu, act = bf(n_tok, d), bf(ff, d), torch.empty(n_tok, ff, dtype=torch.bfloat16, device=dev)
+        wg, actg = bf(ff, d), torch.empty(n_tok, ff // 2, dtype=torch.bfloat16, device=dev)
+        up_bytes, up_flops = n_tok * d * 2 + ff * d * 2 + n_tok * ff * 2, 2.0 * n_tok * d * ff
+        ms = timed(lambda: kernels.gemm_tc(x, wg, actg, glu="silu"))
+        report(f"gemm_tc gated silu ({ff} rows of weights), {tag}", "-", ms, up_bytes - n_tok * ff, up_flops)
+        ms = timed(lambda: kernels.gemm_tc_unary(x, wu, act, "gelu"))
+        report(f"gemm_tc_unary exact gelu ({ff} rows of weights), {tag}", "gemm_tc gated silu", ms, up_bytes, up_flops)
+        del k_pages, v_pages
+    out["kernels"] = rows
+    out["wait_errors"] = wait_errors(kernels)
+    print(json.dumps(out))
+    return 0
+
+
 def run_workload(args):
     """The two workloads beside the headline one, through ``Engine.generate`` (host token ids in, ids out):
 
@@ -934,12 +1088,12 @@ def main():
                     help="run fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--case", default="full",
                     choices=["full", "prefill", "decode", "workload-1b", "workload-13b", "float32", "reference-kernels",
-                             "tumatar", "tikalix"],
+                             "tumatar", "tikalix", "vilazen"],
                     help="full: the whole measurement; prefill / decode: that phase alone (for profilers and sweeps); "
                          "workload-1b / workload-13b: the two other workloads through Engine.generate; float32: the "
                          "8B shape in true 32-bit; reference-kernels: the reference's CUDA kernels alone, if built; tumatar: the "
                          "Tumatar design beside the Llama shape of the same width (--shape 1b or 8b), and its kernels alone; tikalix: "
-                         "the same for the Tikalix design")
+                         "the same for the Tikalix design; vilazen: the same for the Vilazen design")
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="--case prefill/decode: layer sizes")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="--case prefill/decode")
     ap.add_argument("--repeats", type=int, default=2, help="workload cases: timed repetitions after one warm-up")
@@ -965,6 +1119,8 @@ def main():
         return run_tumatar(args)
     if args.case == "tikalix":
         return run_tikalix(args)
+    if args.case == "vilazen":
+        return run_vilazen(args)
     if args.case != "full":
         return run_case(args)
     return run_ours(args)

@@ -155,6 +155,48 @@ def test_attention_with_a_window_kept_first_tokens_and_sinks(dtype, H, G, hd, wi
 
 
 @pytest.mark.parametrize("dtype", TYPES)
+@pytest.mark.parametrize("hd,window,keep,sink", [(64, 100, 130, True), (128, 200, 64, False), (64, 65, 1, False),
+                                                 (64, 300, 129, True)])
+def test_a_late_portion_of_a_prompt_reads_the_kept_pages_and_its_window_only(dtype, hd, window, keep, sink):
+    """The last 100 tokens of a prompt of 700 as a step of their own: the pages between the kept first tokens and the
+    step's first window hold a huge number, which a key read from there would show; the kept pages are one, two and
+    three (a last step of one page) and the window's first page lies right behind them or far away."""
+    from ziglm_b200 import kernels
+    from ziglm_b200.engine.workspace import Workspace
+    from ziglm_b200.parts.base import LayerIO
+    H, G, page, scale, L, new = 4, 2, 64, 0.25, 700, 100
+    kernels.require(("attention",) + kernels.fast_attention_libraries(dtype, hd, H, G, keep_first=keep, sinks=sink))
+    k, v = _r(L, G, hd, seed=1, dtype=dtype), _r(L, G, hd, seed=2, dtype=dtype)
+    q = _r(L, H, hd, seed=3, scale=0.6, dtype=dtype)
+    sinks = (_r(H, seed=5) * 2.0 + 1.0) if sink else None
+    n_pages = -(-L // page)
+    order = [(7 * i + 3) % n_pages for i in range(n_pages)]
+    table = _i32([order])
+    k_pages = torch.zeros(n_pages, G, page, hd, dtype=dtype, device=DEV)
+    v_pages = torch.zeros(n_pages, G, page, hd, dtype=dtype, device=DEV)
+    for pos in range(L):
+        k_pages[order[pos // page], :, pos % page] = k[pos]
+        v_pages[order[pos // page], :, pos % page] = v[pos]
+    past = L - new
+    for i in range(-(-keep // page), (past - window + 1) // page):
+        k_pages[order[i]].fill_(1e4)
+        v_pages[order[i]].fill_(1e4)
+    qf, kf, vf = q.float().cpu(), k.float().cpu(), v.float().cpu()
+    seen = P.visible(torch.arange(past, L), torch.arange(L), window, keep)
+    want = torch.zeros(new, H, hd)
+    for h in range(H):
+        s_ = (qf[past:, h] @ kf[:, h // (H // G)].t()) * scale
+        want[:, h] = P.softmax_rows(s_, seen, sinks[h].cpu() if sink else None) @ vf[:, h // (H // G)]
+    step = SimpleNamespace(n_tokens=new, n_seqs=1, single_token=False, max_new=new, max_total=L,
+                           positions=_i32(list(range(past, L))), seq_of_token=_i32([0] * new), cu_seqlens=_i32([0, new]),
+                           past_lens=_i32([past]), total_lens=_i32([L]), ws=Workspace(torch.device(DEV)))
+    out = torch.empty(new, H * hd, dtype=dtype, device=DEV)
+    kernels.attention(step, q[past:].reshape(new, H * hd).contiguous(), out, H, G, hd, scale, window,
+                      LayerIO(k_pages=k_pages, v_pages=v_pages, block_table=table, page_size=page), keep_first=keep, sinks=sinks)
+    torch.testing.assert_close(out.float().cpu(), want.reshape(new, H * hd), **_tol(dtype, (2e-5, 1e-4), (2e-2, 2e-2)))
+
+
+@pytest.mark.parametrize("dtype", TYPES)
 @pytest.mark.parametrize("H,D,V,decay", [(3, 12, 20, [0.5, 0.9, 1.0]), (2, 64, 64, [0.999, 0.97]), (1, 5, 3, [1.0]),
                                           (2, 33, 35, [0.3, 0.95]), (4, 128, 32, [0.6, 0.88, 0.97, 0.999])])
 def test_decayed_linear_attention_over_steps_with_slots_used_again(dtype, H, D, V, decay):

@@ -1,4 +1,4 @@
-"""config.json dictionaries of a few members of the Llama family, for models with random weights.
+"""config.json dictionaries of a few members of the Llama family and of the other designs, for models with random weights.
 
 The reference's ``synthetic`` stage writes one fixed 2-layer sample (src/synthetic.zig:9-18); these are the
 shapes the measurements of this library name, so that the command line and ``bench.py`` agree on them.
@@ -7,6 +7,7 @@ No checkpoint is read: ``Engine.from_config`` fills the weights from a seed.
 from __future__ import annotations
 
 import copy
+import math
 from typing import Any, Dict
 
 
@@ -86,6 +87,34 @@ def _tikalix(width: int, vocab: int, pairs: int, heads: int, kv_heads: int, dim:
 
 SHAPES["tikalix-1b"] = _tikalix(2048, 128256, 8, 32, 8, 64, 8192, 16, 2048)
 SHAPES["tikalix-8b"] = _tikalix(4096, 128256, 16, 32, 8, 128, 14336, 16, 3584)
+
+
+def _vilazen(width: int, vocab: int, groups: int, heads: int, kv_heads: int, dim: int, ff: int) -> Dict[str, Any]:
+    """A Vilazen stack of ``groups`` times (side-by-side attention and decayed linear attention, windowed attention
+    with mixed values, latent attention, windowed attention with mixed values) with the heads of the Llama shape of
+    that width: keys and values of one size, half of every head rotated, windows of 1,024 positions that keep the
+    first 64, a key/value latent of 96 beside 32 rotated dimensions (what the tensor-core attention takes), linear
+    attention over heads of 128 with decays between exp(-1/4) and exp(-1/1024)."""
+    rot = {"dims": dim // 2, "base": 500000.0}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": dict(rot),
+           "mask": {"size": 1024, "keep_first": 64}, "v_mix": True}
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": dict(rot)}
+    lin_heads = width // 256
+    right = {"heads": lin_heads, "dim": 128, "vdim": 128,
+             "decay": [math.exp(-1.0 / 4.0 ** (1 + 4.0 * i / max(1, lin_heads - 1))) for i in range(lin_heads)]}
+    lat = {"heads": width // 128, "dim": 96, "rot_dim": 32, "vdim": 128, "kv_rank": 96, "scale": 128 ** -0.5,
+           "rot": {"dims": 32, "base": 500000.0}, "mask": {"size": 1024}}
+    mlp = {"kind": "dense", "ff": ff}
+    four = ({"type": "parallel", "mixer": {"left": left, "left_scale": 1.0, "right": right, "right_scale": 1.0}, "mlp": mlp},
+            {"type": "attention", "mixer": att, "mlp": mlp},
+            {"type": "latent_attention", "mixer": lat, "mlp": mlp},
+            {"type": "attention", "mixer": att, "mlp": mlp})
+    return {"architecture": "Vilazen", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [copy.deepcopy(x) for _ in range(groups) for x in four]}
+
+
+SHAPES["vilazen-1b"] = _vilazen(2048, 128256, 4, 32, 8, 64, 8192)
+SHAPES["vilazen-8b"] = _vilazen(4096, 128256, 8, 32, 8, 128, 14336)
 
 
 def shape(name: str) -> Dict[str, Any]:

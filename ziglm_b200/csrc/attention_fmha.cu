@@ -68,6 +68,8 @@ struct FmArgs {
     float cap_in2;       // soft cap c > 0: 2 log2(e) * scale / c, so that 2^(raw * cap_in2) = exp(2 * raw * scale / c)
     float cap_log2;      // c * log2(e), or 0: no cap
     int window;
+    int keep_first;      // with a window: the first positions of a sequence that stay visible behind it
+    const float* sinks;  // one number per query head in the softmax's denominator (already times log2(e)), or null
     const int* block_table;
     int bt_stride;
     const int* cu_seqlens;
@@ -78,8 +80,9 @@ struct FmArgs {
 // The softmax of one query row over a step of NP pages: S from tensor memory, P (bf16) back over its first
 // half.  Returns the factor by which the running sum was rescaled; updates m (reference maximum, base 2) and l.
 template <int HD, int NP>
-__device__ __forceinline__ float softmax_row(uint32_t t_s, uint32_t t_o, bool full, int lo_vis, int hi_vis, float scale,
-                                             float neg_big, int lt, float& m, float& l, float cap_in2, float cap_log2) {
+__device__ __forceinline__ float softmax_row(uint32_t t_s, uint32_t t_o, bool full, int lo_vis, int hi_vis, int keep_vis,
+                                             float scale, float neg_big, int lt, float& m, float& l, float cap_in2,
+                                             float cap_log2) {
     constexpr int N = NP * FM_PAGE;
     uint32_t v[N];
 #pragma unroll
@@ -106,7 +109,7 @@ __device__ __forceinline__ float softmax_row(uint32_t t_s, uint32_t t_o, bool fu
     } else {
 #pragma unroll
         for (int i = 0; i < N; ++i) {
-            if (i < lo_vis || i > hi_vis) v[i] = __float_as_uint(neg_big);      // stays masked below
+            if ((i < lo_vis && i >= keep_vis) || i > hi_vis) v[i] = __float_as_uint(neg_big);   // stays masked below
             mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(v[i]));
         }
     }
@@ -198,23 +201,43 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const int* bt = a.block_table + (long)b * a.bt_stride;
     // The two tiles: their rows, the positions they span and the pages those see.  Tile 0 always has rows;
     // tile 1 has none when the sequence ends inside tile 0.
-    int rows_t[FM_TILES], pos_last_t[FM_TILES], step_lo[FM_TILES], step_hi[FM_TILES];
-    int page_lo = 0, page_hi = 0;
+    int rows_t[FM_TILES], pos_last_t[FM_TILES], step_lo[FM_TILES], step_hi[FM_TILES], plo_t[FM_TILES], phi_t[FM_TILES];
 #pragma unroll
     for (int t = 0; t < FM_TILES; ++t) {
         rows_t[t] = max(0, min(FM_BQ, n_new - q0 - t * FM_BQ));
         const int pf = past + q0 + t * FM_BQ;
         pos_last_t[t] = pf + max(rows_t[t], 1) - 1;
         const int sf = (a.window > 0 && pf - a.window + 1 > 0) ? pf - a.window + 1 : 0;
-        const int plo = sf / FM_PAGE, phi = pos_last_t[t] / FM_PAGE + 1;
-        if (t == 0) { page_lo = plo; page_hi = phi; }
-        else if (rows_t[t] > 0) page_hi = phi;
-        step_lo[t] = (plo - page_lo) / FM_NP;
-        step_hi[t] = rows_t[t] > 0 ? (phi - page_lo + FM_NP - 1) / FM_NP : 0;
-        if (rows_t[t] == 0) step_lo[t] = 0;
+        plo_t[t] = sf / FM_PAGE;
+        phi_t[t] = pos_last_t[t] / FM_PAGE + 1;
     }
-    const int n_pages = page_hi - page_lo;
-    const int n_steps = (n_pages + FM_NP - 1) / FM_NP;            // steps of two pages; the last may hold one
+    int page_lo = plo_t[0];
+    const int page_hi = rows_t[1] > 0 ? phi_t[1] : phi_t[0];
+    // The first positions a window keeps: their pages come first, in steps of their own (the last may hold one
+    // page), when the window's pages begin behind them; when the two touch, the block reads from page 0 on and the
+    // mask alone tells the kept keys from the ones between.
+    const int keep = a.window > 0 ? a.keep_first : 0;
+    const int kept_pages = (keep + FM_PAGE - 1) / FM_PAGE;
+    int kept_steps = 0;
+    bool joined = false;
+    if (kept_pages > 0) {
+        if (page_lo > kept_pages) kept_steps = (kept_pages + FM_NP - 1) / FM_NP;
+        else { page_lo = 0; joined = true; }
+    }
+#pragma unroll
+    for (int t = 0; t < FM_TILES; ++t) {
+        step_lo[t] = rows_t[t] > 0 ? kept_steps + (joined ? 0 : (plo_t[t] - page_lo) / FM_NP) : 0;
+        step_hi[t] = rows_t[t] > 0 ? kept_steps + (phi_t[t] - page_lo + FM_NP - 1) / FM_NP : 0;
+    }
+    const int n_pages = page_hi - page_lo;                        // the window's pages
+    const int n_steps = kept_steps + (n_pages + FM_NP - 1) / FM_NP;   // steps of two pages; the last of a range may hold one
+    auto pages_of = [&](int j) {
+        return j < kept_steps ? min(FM_NP, kept_pages - j * FM_NP) : min(FM_NP, n_pages - (j - kept_steps) * FM_NP);
+    };
+    auto first_page_of = [&](int j) { return j < kept_steps ? j * FM_NP : page_lo + (j - kept_steps) * FM_NP; };
+    // tile t works on step j; its count of steps before j
+    auto runs = [&](int t, int j) { return j >= 0 && rows_t[t] > 0 && (j < kept_steps || (j >= step_lo[t] && j < step_hi[t])); };
+    auto local_step = [&](int t, int j) { return j < kept_steps ? j : kept_steps + j - step_lo[t]; };
 
     if (threadIdx.x == 0) {
         prefetch_tmap(&tmap_q);
@@ -257,9 +280,9 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
             int issued = 0;
             bool alive = true;
             for (int j = 0; j < n_steps && alive; ++j, ++issued) {
-                const int np = min(FM_NP, n_pages - j * FM_NP);
+                const int np = pages_of(j);
                 int rows[FM_NP];
-                for (int pg = 0; pg < np; ++pg) rows[pg] = (bt[page_lo + j * FM_NP + pg] * a.n_kv + kvh) * FM_PAGE;
+                for (int pg = 0; pg < np; ++pg) rows[pg] = (bt[first_page_of(j) + pg] * a.n_kv + kvh) * FM_PAGE;
                 // keys: per 64-dim chunk the pages lie one after the other, so the step's keys are rows 0..127 of
                 // one K-major tile; values: page after page, each an MN-major tile of its own
                 const int sk = j % C::NK;
@@ -313,15 +336,15 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                 for (int t = 0; t < FM_TILES; ++t) {
                     if (!alive) break;
                     const int jj = j - 1;
-                    if (jj >= step_lo[t] && jj < step_hi[t]) {
-                        const int sv = jj % C::NV, lt = jj - step_lo[t];
+                    if (runs(t, jj)) {
+                        const int sv = jj % C::NV, lt = local_step(t, jj);
                         if (!mbar_wait(v_full0 + 8 * sv, (jj / C::NV) & 1, abort_flag, a.err, ERR_FM_KV) ||
                             !mbar_wait(p_full0 + 8 * t, lt & 1, abort_flag, a.err, ERR_FM_P)) {
                             alive = false;
                             break;
                         }
                         tc_fence_after_sync();
-                        const int np = min(FM_NP, n_pages - jj * FM_NP);
+                        const int np = pages_of(jj);
                         const uint32_t tmem_o = tmem_base + C::O_COL + t * HD;
                         const uint32_t tmem_p = tmem_base + C::S_COL + t * FM_KEYS;
                         for (int pg = 0; pg < np; ++pg) {
@@ -335,7 +358,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                         }
                         if (jj == step_hi[t] - 1) umma_commit(o_full0 + 8 * t);
                     }
-                    if (j >= step_lo[t] && j < step_hi[t]) {
+                    if (j < n_steps && runs(t, j)) {
                         const int sk = j % C::NK;
                         if (!mbar_wait(k_full0 + 8 * sk, (j / C::NK) & 1, abort_flag, a.err, ERR_FM_KV)) {
                             alive = false;
@@ -343,7 +366,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                         }
                         tc_fence_after_sync();
                         const uint32_t tmem_s = tmem_base + C::S_COL + t * FM_KEYS;
-                        const uint32_t idesc_s = n_pages - j * FM_NP >= FM_NP ? idesc_s2 : idesc_s1;
+                        const uint32_t idesc_s = pages_of(j) >= FM_NP ? idesc_s2 : idesc_s1;
 #pragma unroll
                         for (int ks = 0; ks < HD / 16; ++ks) {
                             const uint64_t da = smem_desc_sw128(q_smem + t * C::Q_BYTES + (ks >> 2) * (FM_BQ * 128) + (ks & 3) * 32);
@@ -375,25 +398,31 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const float scale = a.scale_log2;
         const float neg_big = -3.0e38f;                               // stands for a masked score before scaling
         float m = -INFINITY, l = 0.f;
+        if (a.sinks) {
+            // a number in the denominator that belongs to no key: the row begins with it as its maximum and sum
+            m = a.sinks[h] * 1.4426950408889634f;
+            l = 1.0f;
+        }
         bool alive = true;
-        for (int j = step_lo[t]; j < step_hi[t]; ++j) {
-            const int lt = j - step_lo[t];
+        for (int j = kept_steps > 0 ? 0 : step_lo[t]; j < step_hi[t]; j = (j + 1 == kept_steps ? step_lo[t] : j + 1)) {
+            const int lt = local_step(t, j);
             alive = warp_mbar_wait(s_full0 + 8 * t, lt & 1, abort_flag, a.err, ERR_FM_S, lane);
             if (!alive) break;
             tc_fence_after_sync();
-            const int np = min(FM_NP, n_pages - j * FM_NP);
-            const int key0 = (page_lo + j * FM_NP) * FM_PAGE;
+            const int np = pages_of(j);
+            const int key0 = first_page_of(j) * FM_PAGE;
             const int key_end = key0 + np * FM_PAGE - 1;               // last key this step really holds
-            const bool full = key0 >= start && key_end <= pos;
-            const int lo_vis = max(start, key0) - key0, hi_vis = min(pos, key_end) - key0;   // visible keys [lo, hi]
+            const bool full = key_end <= pos && (key0 >= start || key_end < keep);
+            // visible keys: [lo, hi], and those before keep_vis (the kept first positions) as far as hi
+            const int lo_vis = max(start, key0) - key0, hi_vis = min(pos, key_end) - key0, keep_vis = keep - key0;
             // One reading of the row: the loads of all its scores are issued together and waited for once
             // (a tcgen05.ld and its wait cost about as much as the arithmetic on 32 scores), the row stays in
             // registers between the maximum and the exponentials, and the stores of P are waited for once.
             float corr;
             if (np == FM_NP)
-                corr = softmax_row<HD, FM_NP>(t_s, t_o, full, lo_vis, hi_vis, scale, neg_big, lt, m, l, a.cap_in2, a.cap_log2);
+                corr = softmax_row<HD, FM_NP>(t_s, t_o, full, lo_vis, hi_vis, keep_vis, scale, neg_big, lt, m, l, a.cap_in2, a.cap_log2);
             else
-                corr = softmax_row<HD, 1>(t_s, t_o, full, lo_vis, hi_vis, scale, neg_big, lt, m, l, a.cap_in2, a.cap_log2);
+                corr = softmax_row<HD, 1>(t_s, t_o, full, lo_vis, hi_vis, keep_vis, scale, neg_big, lt, m, l, a.cap_in2, a.cap_log2);
             (void)corr;
             tmem_st_wait();
             tc_fence_before_sync();
@@ -527,10 +556,11 @@ using namespace zlm;
 
 // Prompt attention: B sequences with cu_seqlens[B+1] new tokens each after past_lens[b] cached ones.
 // q: bf16 [T, q_row_stride], the query heads first in each row; out: bf16 [T, n_heads * hd].
-// softcap c > 0: the scaled scores become c tanh(score / c); 0: none.
+// softcap c > 0: the scaled scores become c tanh(score / c); 0: none.  keep_first: with a window, the first positions
+// of a sequence that stay visible behind it.  sinks: float [n_heads] or null; exp(sinks[h]) joins head h's denominator.
 ZLM_EXPORT int zlm_attention_prefill_fmha(const void* q, long q_row_stride, long total_tokens, void* out, int B,
                                           int max_new, int n_heads, int n_kv, int hd, float scale, float softcap,
-                                          int window, const int* cu_seqlens, const int* past_lens, const int* block_table,
+                                          int window, int keep_first, const float* sinks, const int* cu_seqlens, const int* past_lens, const int* block_table,
                                           int bt_stride, const void* k_pages, const void* v_pages, long n_pages,
                                           int page_size, cudaStream_t stream) {
     if (B <= 0 || max_new <= 0) return 0;
@@ -557,6 +587,8 @@ ZLM_EXPORT int zlm_attention_prefill_fmha(const void* q, long q_row_stride, long
     a.cap_in2 = softcap > 0.f ? 2.0f * 1.4426950408889634f * scale / softcap : 0.f;
     a.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     a.window = window;
+    a.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
+    a.sinks = sinks;
     a.block_table = block_table;
     a.bt_stride = bt_stride;
     a.cu_seqlens = cu_seqlens;

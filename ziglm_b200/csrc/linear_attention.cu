@@ -10,6 +10,15 @@
 // columns): the columns of S are independent of one another, so the tiles of a head need nothing from each other
 // but the scores q_i . k_j, which each computes for itself.  Every product is float FMA in a fixed order: the
 // scores and their weights, the state and the outputs never pass through a 16-bit type.
+//
+// A long prompt is cut into segments of LA_SEG tokens that run side by side (a sequence alone would be a handful
+// of blocks that walk its chunks one after the other):
+//   1. every segment but a sequence's last sums its own tokens into a state that starts at zero;
+//   2. per sequence and head, an element-wise scan turns those into the states the segments start from,
+//      S_(s+1) = a^LA_SEG S_s + local_s;
+//   3. every segment runs the chunked form from its start state; the last one of a sequence writes the state back.
+// The state update is computed twice (steps 1 and 3), which costs a third more arithmetic and buys T / LA_SEG times
+// the blocks.
 #include "common.cuh"
 
 namespace zlm {
@@ -19,6 +28,19 @@ constexpr int LA_VT = 32;         // value columns of a block
 constexpr int LA_THREADS = 256;
 constexpr int LA_WARPS = LA_THREADS / 32;
 constexpr int LA_MAX_D = 512;
+constexpr int LA_SEG = 128;       // tokens of a segment: a multiple of the chunk
+
+// The sequence and the segment of it that block g works on, sequences counted in order with ceil(len / LA_SEG)
+// segments each.  False: g lies behind the last segment.
+__device__ __forceinline__ bool la_find_segment(int g, const int* __restrict__ cu_seqlens, int n_seqs, int& b, int& seg,
+                                                int& n_segs) {
+    for (b = 0; b < n_seqs; ++b) {
+        n_segs = (cu_seqlens[b + 1] - cu_seqlens[b] + LA_SEG - 1) / LA_SEG;
+        if (g < n_segs) { seg = g; return true; }
+        g -= n_segs;
+    }
+    return false;
+}
 
 __device__ __forceinline__ float la_act(float x, int act) { return act == 1 ? x / (1.0f + expf(-x)) : x; }
 
@@ -29,12 +51,18 @@ static inline size_t la_smem_floats(int Dp) {
 }
 
 // pows: float [H][C+1], pows[h][n] = decay_h^n.  state: float [slots][H][D][V].  out: float rows [T][H*V].
-template <typename T>
+// seg_state null: a block owns a whole sequence (blockIdx.x).  Else blockIdx.x counts segments and seg_state is
+// float [segments][H][D][V]: with STATE_ONLY the block leaves the sum of its segment there (started at zero; a
+// sequence's last segment does nothing), without it the block starts from the entry before its own (the scan wrote
+// the segment's start state there; a sequence's first segment starts from ``state``) and only a sequence's last
+// segment writes ``state``.
+template <typename T, bool STATE_ONLY>
 __global__ void __launch_bounds__(LA_THREADS)
 decayed_linear_attention_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_off, int v_off, int H,
                                 int D, int Dp, int V, int act, const float* __restrict__ pows,
                                 float* __restrict__ state, const int* __restrict__ slots,
-                                const int* __restrict__ cu_seqlens, float* __restrict__ out, long out_stride) {
+                                const int* __restrict__ cu_seqlens, int n_seqs, float* __restrict__ seg_state,
+                                float* __restrict__ out, long out_stride) {
     extern __shared__ __align__(16) float la_smem[];
     float* q_s = la_smem;                              // [C][Dp]
     float* kT_s = q_s + LA_C * Dp;                     // [Dp][C+1]
@@ -44,16 +72,26 @@ decayed_linear_attention_kernel(const T* __restrict__ proj, long row_stride, int
     __shared__ float pw[LA_C + 1];
 
     pdl_launch_dependents();
-    const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * LA_VT;
+    const int h = blockIdx.y, v0 = blockIdx.z * LA_VT;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nv = min(LA_VT, V - v0);                 // value columns of this tile
     for (int i = threadIdx.x; i <= LA_C; i += LA_THREADS) pw[i] = pows[h * (LA_C + 1) + i];
     pdl_wait();
-    const int first = cu_seqlens[b], last = cu_seqlens[b + 1];
-    float* st = state + (((long)slots[b] * H + h) * D) * V;
+    int b = blockIdx.x, seg = 0, n_segs = 1;
+    if (seg_state != nullptr && !la_find_segment(blockIdx.x, cu_seqlens, n_seqs, b, seg, n_segs)) return;
+    if (STATE_ONLY && seg == n_segs - 1) return;
+    int first = cu_seqlens[b], last = cu_seqlens[b + 1];
+    if (seg_state != nullptr) {
+        first += seg * LA_SEG;
+        last = min(last, first + LA_SEG);
+    }
+    const long hdv = (long)H * D * V;
+    float* st = state + (((long)slots[b] * H + h) * D) * V;                       // where the sequence's state lives
+    const float* from = seg == 0 ? st : seg_state + (long)(blockIdx.x - 1) * hdv + (long)h * D * V;
+    float* to = STATE_ONLY ? seg_state + (long)blockIdx.x * hdv + (long)h * D * V : st;
     for (int i = threadIdx.x; i < Dp * LA_VT; i += LA_THREADS) {
         const int d = i / LA_VT, v = i % LA_VT;
-        S_s[i] = (d < D && v < nv) ? st[(long)d * V + v0 + v] : 0.f;
+        S_s[i] = (!STATE_ONLY && d < D && v < nv) ? from[(long)d * V + v0 + v] : 0.f;
     }
 
     for (int c0 = first; c0 < last; c0 += LA_C) {
@@ -77,7 +115,7 @@ decayed_linear_attention_kernel(const T* __restrict__ proj, long row_stride, int
         }
         __syncthreads();
         // scores with their decay: a_s[i][j] = a^(i-j) (q_i . k_j) for j <= i.  A thread: rows warp, warp+8, .., column lane.
-        {
+        if (!STATE_ONLY) {
             float s[4] = {0.f, 0.f, 0.f, 0.f};
             for (int d = 0; d < Dp; d += 4) {
                 const float k0 = kT_s[(d + 0) * (LA_C + 1) + lane], k1 = kT_s[(d + 1) * (LA_C + 1) + lane];
@@ -95,9 +133,9 @@ decayed_linear_attention_kernel(const T* __restrict__ proj, long row_stride, int
                 a_s[i * (LA_C + 1) + lane] = lane <= i ? s[r] * pw[i - lane] : 0.f;
             }
         }
-        __syncthreads();
+        if (!STATE_ONLY) __syncthreads();
         // outputs: o_i = sum_j a_s[i][j] v_j + a^(i+1) S^T q_i.  A thread: rows warp, warp+8, .., value column lane.
-        {
+        if (!STATE_ONLY) {
             float o[4] = {0.f, 0.f, 0.f, 0.f}, p[4] = {0.f, 0.f, 0.f, 0.f};
             for (int j = 0; j < n; ++j) {
                 const float vv = v_s[j * LA_VT + lane];
@@ -121,7 +159,7 @@ decayed_linear_attention_kernel(const T* __restrict__ proj, long row_stride, int
                     out[(long)(c0 + i) * out_stride + (long)h * V + v0 + lane] = fmaf(pw[i + 1], p[r], o[r]);
             }
         }
-        __syncthreads();                               // everyone has read the old state and v_s
+        if (!STATE_ONLY) __syncthreads();              // everyone has read the old state and v_s
         // the values weighted for the state: v_j a^(n-1-j)
         for (int i = threadIdx.x; i < LA_C * LA_VT; i += LA_THREADS) {
             const int j = i / LA_VT;
@@ -152,9 +190,34 @@ decayed_linear_attention_kernel(const T* __restrict__ proj, long row_stride, int
         }
     }
     __syncthreads();
+    if (!STATE_ONLY && seg != n_segs - 1) return;      // the next segment starts from what the scan left it
     for (int i = threadIdx.x; i < Dp * LA_VT; i += LA_THREADS) {
         const int d = i / LA_VT, v = i % LA_VT;
-        if (d < D && v < nv) st[(long)d * V + v0 + v] = S_s[i];
+        if (d < D && v < nv) to[(long)d * V + v0 + v] = S_s[i];
+    }
+}
+
+// Step 2: seg_state[g] holds the local sum of segment g (entries of last segments are unused).  Afterwards entry g
+// holds the state segment g + 1 starts from.  One thread an element of [D, V], one block row a (sequence, head).
+__global__ void __launch_bounds__(256)
+la_segment_scan_kernel(const float* __restrict__ pows, const float* __restrict__ state, const int* __restrict__ slots,
+                       const int* __restrict__ cu_seqlens, int n_seqs, int H, int DV, float* __restrict__ seg_state) {
+    pdl_launch_dependents();
+    const int b = blockIdx.x, h = blockIdx.y, e = blockIdx.z * blockDim.x + threadIdx.x;
+    pdl_wait();
+    if (e >= DV) return;
+    int g0 = 0;                                        // the sequence's first segment
+    for (int i = 0; i < b; ++i) g0 += (cu_seqlens[i + 1] - cu_seqlens[i] + LA_SEG - 1) / LA_SEG;
+    const int n_segs = (cu_seqlens[b + 1] - cu_seqlens[b] + LA_SEG - 1) / LA_SEG;
+    if (n_segs < 2) return;
+    const float ac = pows[h * (LA_C + 1) + LA_C];      // the decay over a chunk, applied chunk by chunk as step 3 does
+    float run = state[((long)slots[b] * H + h) * DV + e];
+    for (int s = 0; s + 1 < n_segs; ++s) {
+        float* p = seg_state + ((long)(g0 + s) * H + h) * DV + e;
+#pragma unroll
+        for (int c = 0; c < LA_SEG / LA_C; ++c) run *= ac;
+        run += *p;
+        *p = run;
     }
 }
 
@@ -168,30 +231,56 @@ ZLM_EXPORT int zlm_linear_attention_chunk() { return LA_C; }
 // proj: rows [T][row_stride] of the step's type; head h's query lies at columns q_off + h*D, its key at k_off + h*D,
 // its value at v_off + h*V.  act 0: as they are, 1: through silu.  pows: float [H][chunk + 1] with decay_h^n.
 // state: float [n_slots][H][D][V]; slots, cu_seqlens: the step's sequences.  out: float rows [T][out_stride].
-ZLM_EXPORT int zlm_decayed_linear_attention(const void* proj, int dtype, long row_stride, int q_off, int k_off, int v_off,
-                                            int H, int D, int V, int act, const float* pows, float* state,
-                                            const int* slots, const int* cu_seqlens, int n_seqs, float* out,
-                                            long out_stride, cudaStream_t stream) {
-    if (n_seqs <= 0) return 0;
-    if (H <= 0 || D <= 0 || V <= 0 || (act != 0 && act != 1)) return ZLM_ERR_BAD_ARG;
-    if (D > LA_MAX_D || H > 65535 || (V + LA_VT - 1) / LA_VT > 65535) return ZLM_ERR_UNSUPPORTED;
+// seg_state: null, or float [zlm_linear_attention_segments(T, n_seqs)][H][D][V] of scratch, with which the step's T
+// tokens run as segments side by side (three launches instead of one).
+template <typename T>
+static int la_launch(const T* proj, long row_stride, int q_off, int k_off, int v_off, int H, int D, int V, int act,
+                     const float* pows, float* state, const int* slots, const int* cu_seqlens, int n_seqs,
+                     int n_segments, float* seg_state, float* out, long out_stride, cudaStream_t stream) {
     const int Dp = (D + 3) / 4 * 4;
     const size_t smem = la_smem_floats(Dp) * sizeof(float);
-    dim3 grid(n_seqs, H, (V + LA_VT - 1) / LA_VT);
+    const int v_tiles = (V + LA_VT - 1) / LA_VT;
+    auto full = decayed_linear_attention_kernel<T, false>;
+    auto local = decayed_linear_attention_kernel<T, true>;
     cudaError_t e;
-    if (dtype == ZLM_F32) {
-        auto kernel = decayed_linear_attention_kernel<float>;
-        if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
-            return (int)e;
-        e = launch_pdl(kernel, grid, dim3(LA_THREADS), smem, stream, (const float*)proj, row_stride, q_off, k_off, v_off, H,
-                       D, Dp, V, act, pows, state, slots, cu_seqlens, out, out_stride);
-    } else if (dtype == ZLM_BF16) {
-        auto kernel = decayed_linear_attention_kernel<__nv_bfloat16>;
-        if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
-            return (int)e;
-        e = launch_pdl(kernel, grid, dim3(LA_THREADS), smem, stream, (const __nv_bfloat16*)proj, row_stride, q_off, k_off,
-                       v_off, H, D, Dp, V, act, pows, state, slots, cu_seqlens, out, out_stride);
-    } else
-        return ZLM_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024) {
+        if ((e = cudaFuncSetAttribute(full, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
+        if ((e = cudaFuncSetAttribute(local, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
+    }
+    if (seg_state == nullptr) {
+        e = launch_pdl(full, dim3(n_seqs, H, v_tiles), dim3(LA_THREADS), smem, stream, proj, row_stride, q_off, k_off, v_off,
+                       H, D, Dp, V, act, pows, state, slots, cu_seqlens, n_seqs, (float*)nullptr, out, out_stride);
+        return e == cudaSuccess ? launch_status() : (int)e;
+    }
+    dim3 grid(n_segments, H, v_tiles);
+    e = launch_pdl(local, grid, dim3(LA_THREADS), smem, stream, proj, row_stride, q_off, k_off, v_off, H, D, Dp, V, act,
+                   pows, state, slots, cu_seqlens, n_seqs, seg_state, out, out_stride);
+    if (e != cudaSuccess) return (int)e;
+    e = launch_pdl(la_segment_scan_kernel, dim3(n_seqs, H, (D * V + 255) / 256), dim3(256), 0, stream, pows,
+                   (const float*)state, slots, cu_seqlens, n_seqs, H, D * V, seg_state);
+    if (e != cudaSuccess) return (int)e;
+    e = launch_pdl(full, grid, dim3(LA_THREADS), smem, stream, proj, row_stride, q_off, k_off, v_off, H, D, Dp, V, act, pows,
+                   state, slots, cu_seqlens, n_seqs, seg_state, out, out_stride);
     return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+// An upper bound of the segments of a step of n_tokens tokens in n_seqs sequences: the entries ``seg_state`` needs.
+ZLM_EXPORT int zlm_linear_attention_segments(int n_tokens, int n_seqs) { return n_tokens / LA_SEG + n_seqs; }
+ZLM_EXPORT int zlm_linear_attention_segment() { return LA_SEG; }
+
+ZLM_EXPORT int zlm_decayed_linear_attention(const void* proj, int dtype, long row_stride, int q_off, int k_off, int v_off,
+                                            int H, int D, int V, int act, const float* pows, float* state,
+                                            const int* slots, const int* cu_seqlens, int n_seqs, int n_tokens,
+                                            float* seg_state, float* out, long out_stride, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (H <= 0 || D <= 0 || V <= 0 || (act != 0 && act != 1)) return ZLM_ERR_BAD_ARG;
+    if (D > LA_MAX_D || H > 65535 || (V + LA_VT - 1) / LA_VT > 65535 || n_seqs > 65535) return ZLM_ERR_UNSUPPORTED;
+    const int n_segments = zlm_linear_attention_segments(n_tokens, n_seqs);
+    if (dtype == ZLM_F32)
+        return la_launch((const float*)proj, row_stride, q_off, k_off, v_off, H, D, V, act, pows, state, slots, cu_seqlens,
+                         n_seqs, n_segments, seg_state, out, out_stride, stream);
+    if (dtype == ZLM_BF16)
+        return la_launch((const __nv_bfloat16*)proj, row_stride, q_off, k_off, v_off, H, D, V, act, pows, state, slots,
+                         cu_seqlens, n_seqs, n_segments, seg_state, out, out_stride, stream);
+    return ZLM_ERR_UNSUPPORTED;
 }

@@ -83,8 +83,10 @@ _PROTOTYPES = {
     },
     "linear_attention": {
         "zlm_linear_attention_chunk": [],
+        "zlm_linear_attention_segment": [],
+        "zlm_linear_attention_segments": [c_int, c_int],
         "zlm_decayed_linear_attention": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                         c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_long, c_void_p],
+                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_long, c_void_p],
     },
     "moe": {
         "zlm_moe_route": [c_void_p, c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -130,8 +132,8 @@ _PROTOTYPES = {
     },
     "attention_fmha": {
         "zlm_attention_prefill_fmha": [c_void_p, c_long, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                       c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int,
-                                       c_void_p],
+                                       c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                       c_void_p, c_long, c_int, c_void_p],
         "zlm_attention_fmha_status": [c_void_p],
         "zlm_attention_fmha_wait_selftest": [c_int, c_void_p, c_void_p],
     },
@@ -785,7 +787,9 @@ def decayed_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: 
     """Linear attention with a fixed decay per head over the step's sequences: per head S <- a S + k v^T (float32
     [dim, value_dim], carried in ``state`` [slots, n_heads, dim, value_dim]) and o = S^T q.  Head h's q, k, v are the
     columns q_off + h*dim, k_off + h*dim, v_off + h*value_dim of ``proj``'s rows, read through ``activation``
-    (None or "silu").  ``pows`` float32 [n_heads, chunk + 1]: decay_h^n.  ``out`` float32 [T, n_heads * value_dim]."""
+    (None or "silu").  ``pows`` float32 [n_heads, chunk + 1]: decay_h^n.  ``out`` float32 [T, n_heads * value_dim].
+    A step with a sequence of more tokens than a segment runs its segments side by side, with their start states in
+    the step's scratch."""
     _rows(proj, "proj"); _rows(out, "out"); _cuda(pows, "pows", torch.float32); _cuda(state, "state", torch.float32)
     T = proj.shape[0]
     if activation not in (None, "silu"):
@@ -799,10 +803,15 @@ def decayed_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: 
         raise KernelError("decayed_linear_attention: the state must be [slots, heads, dim, value_dim]")
     if tuple(pows.shape) != (n_heads, linear_attention_chunk() + 1) or not pows.is_contiguous():
         raise KernelError("decayed_linear_attention: the table of powers must be [heads, chunk + 1]")
+    seg_state = None
+    if not step.single_token and step.max_new > int(_fn("linear_attention", "zlm_linear_attention_segment")()):
+        n = int(_fn("linear_attention", "zlm_linear_attention_segments")(T, step.n_seqs))
+        seg_state = step.ws.buf("lin_segment_states", (n, n_heads, dim, value_dim), torch.float32)
     _check(_fn("linear_attention", "zlm_decayed_linear_attention")(
         proj.data_ptr(), code(proj.dtype), _row_stride(proj), q_off, k_off, v_off, n_heads, dim, value_dim,
         1 if activation == "silu" else 0, pows.data_ptr(), state.data_ptr(), step.slots.data_ptr(),
-        step.cu_seqlens.data_ptr(), step.n_seqs, out.data_ptr(), _row_stride(out), _stream()), "decayed_linear_attention")
+        step.cu_seqlens.data_ptr(), step.n_seqs, T, _ptr(seg_state), out.data_ptr(), _row_stride(out), _stream()),
+        "decayed_linear_attention")
 
 
 def attention_general_scratch(n_tokens: int, n_heads: int, n_kv: int, head_dim: int, max_keys: int) -> int:
@@ -1011,9 +1020,15 @@ def attention_prefill(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new
 def attention_prefill_fmha(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, max_new: int, n_heads: int, n_kv: int,
                            head_dim: int, scale: float, window: Optional[int], cu_seqlens: torch.Tensor,
                            past_lens: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
-                           v_pages: torch.Tensor, page_size: int, softcap: float = 0.0) -> bool:
+                           v_pages: torch.Tensor, page_size: int, softcap: float = 0.0, keep_first: int = 0,
+                           sinks: Optional[torch.Tensor] = None) -> bool:
     """Prompt attention on the tcgen05 tensor cores (tiles of 128 queries, accumulators in tensor memory); same
-    arguments as :func:`attention_prefill`.  False if refused."""
+    arguments as :func:`attention_prefill`, and ``keep_first`` / ``sinks`` as :func:`attention_general` takes them.
+    False if refused."""
+    if sinks is not None:
+        _cuda(sinks, "sinks", torch.float32)
+        if sinks.numel() != n_heads or not sinks.is_contiguous():
+            raise KernelError("attention_prefill_fmha: one sink per query head is needed")
     _cuda(out, "out", torch.bfloat16); _cuda(k_pages, "k_pages", torch.bfloat16); _cuda(v_pages, "v_pages", torch.bfloat16)
     _cuda(cu_seqlens, "cu_seqlens", torch.int32); _cuda(past_lens, "past_lens", torch.int32)
     _cuda(block_table, "block_table", torch.int32)
@@ -1027,8 +1042,9 @@ def attention_prefill_fmha(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, ma
         raise KernelError("attention_prefill_fmha: sequence arrays are too short")
     status = _fn("attention_fmha", "zlm_attention_prefill_fmha")(
         qkv.data_ptr(), qkv.stride(0), qkv.shape[0], out.data_ptr(), n_seqs, max_new, n_heads, n_kv, head_dim, scale,
-        float(softcap or 0.0), int(window or 0), cu_seqlens.data_ptr(), past_lens.data_ptr(), block_table.data_ptr(),
-        block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, _stream())
+        float(softcap or 0.0), int(window or 0), int(keep_first or 0) if window else 0, _ptr(sinks), cu_seqlens.data_ptr(),
+        past_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
+        k_pages.shape[0], page_size, _stream())
     if status == -2:
         return False
     _check(status, "attention_prefill_fmha")
@@ -1093,7 +1109,14 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
     (the caller multiplies when it was not: in a prompt one pass of ``sigmoid_mul`` over coalesced rows costs less
     than the same work in the prompt kernel's epilogue, where every thread walks a row of its own)."""
     keep_first = int(keep_first or 0) if window else 0
-    plain_only = keep_first > 0 or sinks is not None      # the tensor-core kernels know neither
+    # kept first tokens and sinks: the tcgen05 prompt kernel knows both, the other tensor-core kernels neither
+    plain_only = keep_first > 0 or sinks is not None
+    if plain_only and not step.single_token and step.max_new >= 16 and _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim,
+                                                                                        io.page_size):
+        if attention_prefill_fmha(qkv, out, step.n_seqs, step.max_new, n_heads, n_kv, head_dim, scale, window,
+                                  step.cu_seqlens, step.past_lens, io.block_table, io.k_pages, io.v_pages, io.page_size,
+                                  softcap=softcap, keep_first=keep_first, sinks=sinks):
+            return False
     if not plain_only and _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
         n_blocks = attention_decode_flat_blocks(step.n_tokens, n_heads, n_kv, head_dim) if step.single_token else 0
         if n_blocks > 0:
@@ -1134,7 +1157,7 @@ def fast_attention_libraries(dtype: torch.dtype, head_dim: int, n_heads: int = 1
     """The sources of the tensor-core attention kernels if they take this shape and these options, else nothing (the
     plain kernel runs)."""
     if keep_first or sinks:
-        return ()
+        return ("attention_fmha",) if _tc_attention_ok(dtype, n_heads, n_kv, head_dim, 64) else ()
     return ("attention_tc", "attention_fmha") if _tc_attention_ok(dtype, n_heads, n_kv, head_dim, 64) else ()
 
 
