@@ -196,6 +196,16 @@ def test_a_late_portion_of_a_prompt_reads_the_kept_pages_and_its_window_only(dty
     torch.testing.assert_close(out.float().cpu(), want.reshape(new, H * hd), **_tol(dtype, (2e-5, 1e-4), (2e-2, 2e-2)))
 
 
+def _lin_step(slots, new):
+    """What the linear attention reads of a step: its sequences' slots and token counts, and scratch."""
+    from ziglm_b200.engine.workspace import Workspace
+    cu = [0]
+    for n in new:
+        cu.append(cu[-1] + n)
+    return SimpleNamespace(n_seqs=len(new), slots=_i32(slots), cu_seqlens=_i32(cu), single_token=all(n == 1 for n in new),
+                           max_new=max(new), ws=Workspace(torch.device(DEV)))
+
+
 @pytest.mark.parametrize("dtype", TYPES)
 @pytest.mark.parametrize("H,D,V,decay", [(3, 12, 20, [0.5, 0.9, 1.0]), (2, 64, 64, [0.999, 0.97]), (1, 5, 3, [1.0]),
                                           (2, 33, 35, [0.3, 0.95]), (4, 128, 32, [0.6, 0.88, 0.97, 0.999])])
@@ -229,14 +239,41 @@ def test_decayed_linear_attention_over_steps_with_slots_used_again(dtype, H, D, 
     for new in ([1, 70, 131], [2, 33, 1], [1, 1, 1], [1, 1, 1], [1, 1, 1], [1, 1, 1]):
         proj = torch.cat([f[a:a + n] for f, a, n in zip(full, at, new)]).contiguous()
         T = proj.shape[0]
-        cu = [0, new[0], new[0] + new[1], T]
-        step = SimpleNamespace(n_seqs=3, slots=_i32(slots), cu_seqlens=_i32(cu))
+        step = _lin_step(slots, new)
         out = torch.full((T, H * V), 3.0, device=DEV)
         kernels.decayed_linear_attention(proj, 0, H * D, 2 * H * D, H, D, V, "silu", pows, state, step, out)
         ref = torch.cat([w[a:a + n] for w, a, n in zip(want, at, new)])
         torch.testing.assert_close(out.cpu(), ref, atol=2e-4, rtol=2e-4)
         at = [a + n for a, n in zip(at, new)]
     assert (state[1] == 7.0).all() and (state[4] == 7.0).all()                   # other slots are left alone
+
+
+@pytest.mark.parametrize("dtype", TYPES)
+def test_segments_of_long_prompts_side_by_side(dtype):
+    """Five prompts of 1, 128, 129, 600 and 256 tokens in one step (one, one, two, five and two segments), each on top
+    of a state that is not zero, against the same prompts one after the other in steps of at most a segment."""
+    from ziglm_b200 import kernels
+    kernels.require(("linear_attention",))
+    H, D, V, decay = 3, 20, 40, [0.99, 0.7, 1.0]
+    lens = [1, 128, 129, 600, 256]
+    rows = [_r(L, 2 * H * D + H * V, seed=20 + i, scale=0.5, dtype=dtype) for i, L in enumerate(lens)]
+    chunk = kernels.linear_attention_chunk()
+    pows = torch.tensor([[a ** n for n in range(chunk + 1)] for a in decay], dtype=torch.float64).float().to(DEV)
+    start = _r(len(lens), H, D, V, seed=9)
+    state = torch.cat([start, start]).contiguous()
+    together = torch.empty(sum(lens), H * V, device=DEV)
+    kernels.decayed_linear_attention(torch.cat(rows).contiguous(), 0, H * D, 2 * H * D, H, D, V, "silu", pows, state,
+                                     _lin_step(list(range(len(lens))), lens), together)
+    alone = []
+    for i, r in enumerate(rows):
+        out = torch.empty(r.shape[0], H * V, device=DEV)
+        for t0 in range(0, r.shape[0], 100):
+            part = r[t0:t0 + 100].contiguous()
+            kernels.decayed_linear_attention(part, 0, H * D, 2 * H * D, H, D, V, "silu", pows, state,
+                                             _lin_step([len(lens) + i], [part.shape[0]]), out[t0:t0 + 100])
+        alone.append(out)
+    torch.testing.assert_close(together, torch.cat(alone), atol=1e-3, rtol=2e-4)
+    torch.testing.assert_close(state[:len(lens)], state[len(lens):], atol=1e-3, rtol=2e-4)
 
 
 @pytest.mark.parametrize("dtype", TYPES)
@@ -251,11 +288,12 @@ def test_a_long_prompt_of_linear_attention_against_token_by_token(dtype):
     state = torch.zeros(2, H, D, V, device=DEV)
     whole = torch.empty(1000, H * V, device=DEV)
     kernels.decayed_linear_attention(rows, 0, H * D, 2 * H * D, H, D, V, None, pows, state,
-                                     SimpleNamespace(n_seqs=1, slots=_i32([0]), cu_seqlens=_i32([0, 1000])), whole)
+                                     _lin_step([0], [1000]), whole)
     single = torch.empty(1000, H * V, device=DEV)
+    one = _lin_step([1], [1])
     for t in range(1000):
         kernels.decayed_linear_attention(rows[t:t + 1], 0, H * D, 2 * H * D, H, D, V, None, pows, state,
-                                         SimpleNamespace(n_seqs=1, slots=_i32([1]), cu_seqlens=_i32([0, 1])), single[t:t + 1])
+                                         one, single[t:t + 1])
     torch.testing.assert_close(whole, single, atol=1e-3, rtol=2e-4)
     torch.testing.assert_close(state[0], state[1], atol=1e-3, rtol=2e-4)
 
