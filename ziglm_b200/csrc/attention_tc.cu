@@ -200,6 +200,7 @@ struct AtcCommon {
     float cap_in2;       // soft cap c > 0: 2 log2(e) * scale / c; else 0
     float cap_log2;      // c * log2(e), or 0: no cap
     int window;
+    int keep_first;      // the split decode kernel only: with a window, the first positions that stay visible behind it
     const int* block_table;
     int bt_stride;
     int* err;
@@ -209,17 +210,19 @@ struct AtcCommon {
     long gate_stride;
 };
 
-// The producer warp: copies the pages [page_lo, page_hi) of one kv head into the ring.
+// The producer warp: copies the pages [page_lo, page_hi) of one kv head into the ring.  The numbers count a list
+// that leaves pages out: entry p stands for page p below skip_at and for page p + skip_by from there on.
 template <int HD, typename C>
 __device__ __forceinline__ void produce_pages(const CUtensorMap* tk, const CUtensorMap* tv, const int* bt, int n_kv,
                                               int kvh, int page_lo, int page_hi, uint32_t k0, uint32_t v0,
-                                              uint32_t full0, uint32_t empty0, volatile int* abort_flag, int* err) {
+                                              uint32_t full0, uint32_t empty0, volatile int* abort_flag, int* err,
+                                              int skip_at = 0, int skip_by = 0) {
     int issued = 0;
     for (int p = page_lo; p < page_hi; ++p, ++issued) {
         const int s = issued % C::STAGES;
         const uint32_t ph = (issued / C::STAGES) & 1;
         if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag, err, ERR_ATT_EMPTY)) break;
-        const int row = (bt[p] * n_kv + kvh) * PAGE;
+        const int row = (bt[p < skip_at ? p : p + skip_by] * n_kv + kvh) * PAGE;
         mbar_expect_tx(full0 + 8 * s, 2 * C::TILE_BYTES);
 #pragma unroll
         for (int b = 0; b < HD / 64; ++b) {
@@ -261,9 +264,14 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
     const int* bt = a.block_table + (long)seq_of_token[t] * a.bt_stride;
     const int first_page = start / PAGE, end_page = pos / PAGE + 1;
-    const int per = (end_page - first_page + n_splits - 1) / n_splits;
-    const int page_lo = first_page + split * per;
-    const int page_hi = min(end_page, page_lo + per);
+    // the list of pages: those of the kept first positions that lie before the window's first page, then the window's
+    const int keep = a.window > 0 ? a.keep_first : 0;
+    const int kept_pages = min((keep + PAGE - 1) / PAGE, first_page);
+    const int skip_by = first_page - kept_pages;
+    const int n_list = kept_pages + end_page - first_page;
+    const int per = (n_list + n_splits - 1) / n_splits;
+    const int page_lo = split * per;
+    const int page_hi = min(n_list, page_lo + per);
 
     if (threadIdx.x == 0) {
         prefetch_tmap(&tmap_k);
@@ -290,7 +298,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     if (warp == ATC_CONSUMERS) {
         if (lane == 0)
             produce_pages<HD, C>(&tmap_k, &tmap_v, bt, a.n_kv, kvh, page_lo, page_hi, k0, v0, full0, empty0, abort_flag,
-                              a.err);
+                              a.err, kept_pages, skip_by);
         __syncwarp();
     } else {
         // rows of the tile: the query heads of this kv head (rows beyond the group are zero)
@@ -299,15 +307,30 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
         load_q_frags<HD>(qf, gid < group ? qrow + gid * HD : nullptr, gid + 8 < group ? qrow + (gid + 8) * HD : nullptr,
                          tid4);
         int it = 0;
-        for (int p = page_lo; p < page_hi; ++p, ++it) {
+        for (int lp = page_lo; lp < page_hi; ++lp, ++it) {
+            const int p = lp < kept_pages ? lp : lp + skip_by;
             const int s = it % C::STAGES;
             if (!mbar_wait(full0 + 8 * s, (it / C::STAGES) & 1, abort_flag, a.err, ERR_ATT_FULL)) break;
-            if (p * PAGE >= start && p * PAGE + PAGE - 1 <= pos)
+            if (p * PAGE >= start && p * PAGE + PAGE - 1 <= pos) {
                 page_step<HD, 2, true>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16,
                                        pos, pos, start, start, a.scale_log2, a.cap_in2, a.cap_log2, m, l, o, lane);
-            else
-                page_step<HD, 2, false>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16,
-                                        pos, pos, start, start, a.scale_log2, a.cap_in2, a.cap_log2, m, l, o, lane);
+            } else {
+                // a page that begins before the window: its kept keys [0, keep) and its keys from the window's first
+                // on, as one range when the two touch and else one after the other
+                const bool kept = p * PAGE < keep && p * PAGE < start;
+                const bool seen = p * PAGE + PAGE - 1 >= start;
+                const bool joined = kept && seen && keep >= start;
+                if (kept && !joined) {
+                    const int lim = min(pos, keep - 1);
+                    page_step<HD, 2, false>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16,
+                                            lim, lim, 0, 0, a.scale_log2, a.cap_in2, a.cap_log2, m, l, o, lane);
+                }
+                if (seen) {
+                    const int st = joined ? 0 : start;
+                    page_step<HD, 2, false>(qf, k0 + s * C::TILE_BYTES, v0 + s * C::TILE_BYTES, warp * 16, p * PAGE + warp * 16,
+                                            pos, pos, st, st, a.scale_log2, a.cap_in2, a.cap_log2, m, l, o, lane);
+                }
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(empty0 + 8 * s);
         }
@@ -357,13 +380,16 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
 }
 
 // out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in order.
+// sinks (float, one per head, or null): exp(sinks[h]) joins the denominator of head h.
 template <int HD>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                  __nv_bfloat16* __restrict__ out, int n_splits) {
+                                  __nv_bfloat16* __restrict__ out, int n_splits, const float* __restrict__ sinks = nullptr,
+                                  int n_heads = 1) {
     pdl_launch_dependents();
     pdl_wait();
     const long row = blockIdx.x;                    // t * n_heads + h
-    float big = -INFINITY;
+    const float sink = sinks != nullptr ? sinks[row % n_heads] * 1.4426950408889634f : -INFINITY;
+    float big = sink;
     for (int s = 0; s < n_splits; ++s) big = fmaxf(big, part_ml[(row * n_splits + s) * 2]);
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float acc = 0.f, den = 0.f;
@@ -373,6 +399,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
             acc += part_o[(row * n_splits + s) * HD + d] * wgt;
             den += part_ml[(row * n_splits + s) * 2 + 1] * wgt;
         }
+        if (sinks != nullptr) den += exp2f(sink - big);
         out[row * HD + d] = __float2bfloat16_rn(acc / den);
     }
 }
@@ -1069,6 +1096,7 @@ static int fill_common(AtcCommon* a, CUtensorMap* mk, CUtensorMap* mv, const voi
     a->cap_in2 = softcap > 0.f ? 2.0f * 1.4426950408889634f * scale / softcap : 0.f;
     a->cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
     a->window = window;
+    a->keep_first = 0;
     a->block_table = block_table;
     a->bt_stride = bt_stride;
     a->err = att_error_word();
@@ -1083,8 +1111,11 @@ using namespace zlm;
 
 // Decode-style attention: every token is a tile of its own (its query heads grouped by kv head).
 // part_o: float [T * n_heads * n_splits * hd], part_ml: float [T * n_heads * n_splits * 2] (scratch).
+// keep_first: with a window, the first positions of a sequence that stay visible behind it.  sinks: float [n_heads]
+// or null; exp(sinks[h]) joins head h's denominator.
 ZLM_EXPORT int zlm_attention_decode(const void* q, long q_row_stride, void* out, int T, int n_heads, int n_kv, int hd,
-                                    float scale, float softcap, int window, const int* positions, const int* seq_of_token,
+                                    float scale, float softcap, int window, int keep_first, const float* sinks,
+                                    const int* positions, const int* seq_of_token,
                                     const int* block_table, int bt_stride, const void* k_pages, const void* v_pages,
                                     long n_pages, int page_size, int n_splits, float* part_o, float* part_ml,
                                     cudaStream_t stream) {
@@ -1096,6 +1127,7 @@ ZLM_EXPORT int zlm_attention_decode(const void* q, long q_row_stride, void* out,
     int rc = fill_common(&a, &mk, &mv, q, q_row_stride, n_heads, n_kv, hd, scale, window, block_table, bt_stride,
                          k_pages, v_pages, n_pages, page_size, softcap);
     if (rc) return rc;
+    a.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
     dim3 grid(n_splits, n_kv, T);
     using CFG128 = DecodeCfg<128>;
     using CFG64 = DecodeCfg<64>;
@@ -1107,7 +1139,7 @@ ZLM_EXPORT int zlm_attention_decode(const void* q, long q_row_stride, void* out,
                                    positions, seq_of_token, part_o, part_ml);
         if (e == cudaSuccess)
             e = launch_pdl(attn_merge_kernel<128>, dim3(T * n_heads), dim3(128), 0, stream, (const float*)part_o,
-                           (const float*)part_ml, (__nv_bfloat16*)out, n_splits);
+                           (const float*)part_ml, (__nv_bfloat16*)out, n_splits, sinks, n_heads);
         if (e != cudaSuccess) return (int)e;
     } else {
         static bool done = false;
@@ -1117,7 +1149,7 @@ ZLM_EXPORT int zlm_attention_decode(const void* q, long q_row_stride, void* out,
                                    positions, seq_of_token, part_o, part_ml);
         if (e == cudaSuccess)
             e = launch_pdl(attn_merge_kernel<64>, dim3(T * n_heads), dim3(64), 0, stream, (const float*)part_o,
-                           (const float*)part_ml, (__nv_bfloat16*)out, n_splits);
+                           (const float*)part_ml, (__nv_bfloat16*)out, n_splits, sinks, n_heads);
         if (e != cudaSuccess) return (int)e;
     }
     return launch_status();
@@ -1351,6 +1383,7 @@ ZLM_EXPORT int zlm_attention_decode_noalloc(const void* q, long q_row_stride, vo
     a.cap_in2 = 0.f;
     a.cap_log2 = 0.f;
     a.window = window;
+    a.keep_first = 0;
     a.block_table = block_table;
     a.bt_stride = bt_stride;
     a.err = err;

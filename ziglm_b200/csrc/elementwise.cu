@@ -383,6 +383,28 @@ __global__ void gate_heads_kernel(const T* __restrict__ a, long a_stride, const 
     out[t * out_stride + i] = from_float<T>(to_float(a[t * a_stride + i]) * ((1.0f / (1.0f + expf(-gv))) * mult));
 }
 
+// The same for bf16 rows whose heads, strides and addresses are multiples of 8 elements: 16 bytes a thread.
+__global__ void gate_heads_vec_kernel(const __nv_bfloat16* __restrict__ a, long a_stride, const __nv_bfloat16* __restrict__ g,
+                                      long g_stride, __nv_bfloat16* __restrict__ out, long out_stride, long total8,
+                                      int width8, int n8, float mult) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total8) return;
+    const long t = idx / width8;
+    const int i8 = (int)(idx - t * width8);
+    const float gv = to_float(g[t * g_stride + i8 / n8]);
+    const float f = (1.0f / (1.0f + expf(-gv))) * mult;
+    uint4 av = *reinterpret_cast<const uint4*>(a + t * a_stride + i8 * 8);
+    __nv_bfloat162* ap = reinterpret_cast<__nv_bfloat162*>(&av);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 x = __bfloat1622float2(ap[k]);
+        ap[k] = __floats2bfloat162_rn(x.x * f, x.y * f);
+    }
+    *reinterpret_cast<uint4*>(out + t * out_stride + i8 * 8) = av;
+}
+
 // out[r, i] = x[r, i] / sqrt(mean_i x[r, i]^2 + eps) * w[i] * sigmoid(g[r, i]) * mult: the norm over the concatenated
 // heads of a mixer and its output gate in one pass.  x float rows, g and out rows of the step's type, all with strides
 // of their own.
@@ -401,6 +423,92 @@ __global__ void norm_gate_kernel(const float* __restrict__ x, long x_stride, con
         float y = (xr[i] * inv) * w[i];
         if (g != nullptr) y *= 1.0f / (1.0f + expf(-to_float(g[(long)blockIdx.x * g_stride + i])));
         out[(long)blockIdx.x * out_stride + i] = from_float<T>(y * mult);
+    }
+}
+
+// The same for a bf16 gate and result when the row length, the strides and the addresses are multiples of 4
+// elements: 16 bytes of x, 8 of the gate and 8 of the result a thread and turn.
+__global__ void norm_gate_vec_kernel(const float* __restrict__ x, long x_stride, const float* __restrict__ w,
+                                     const __nv_bfloat16* __restrict__ g, long g_stride, __nv_bfloat16* __restrict__ out,
+                                     long out_stride, int d, float eps, float mult) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float4* xr = reinterpret_cast<const float4*>(x + (long)blockIdx.x * x_stride);
+    const int d4 = d >> 2;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+        const float4 v = xr[i];
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)d + eps);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    for (int i = threadIdx.x; i < d4; i += blockDim.x) {
+        const float4 v = xr[i], ww = wr[i];
+        float y[4] = {(v.x * inv) * ww.x, (v.y * inv) * ww.y, (v.z * inv) * ww.z, (v.w * inv) * ww.w};
+        if (g != nullptr) {
+            const uint2 gv = *reinterpret_cast<const uint2*>(g + (long)blockIdx.x * g_stride + i * 4);
+            const float2 g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.x));
+            const float2 g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv.y));
+            y[0] *= 1.0f / (1.0f + expf(-g0.x)); y[1] *= 1.0f / (1.0f + expf(-g0.y));
+            y[2] *= 1.0f / (1.0f + expf(-g1.x)); y[3] *= 1.0f / (1.0f + expf(-g1.y));
+        }
+        __nv_bfloat162 o0 = __floats2bfloat162_rn(y[0] * mult, y[1] * mult), o1 = __floats2bfloat162_rn(y[2] * mult, y[3] * mult);
+        uint2 ov;
+        ov.x = *reinterpret_cast<uint32_t*>(&o0);
+        ov.y = *reinterpret_cast<uint32_t*>(&o1);
+        *reinterpret_cast<uint2*>(out + (long)blockIdx.x * out_stride + i * 4) = ov;
+    }
+}
+
+// The same for rows of at most 8 elements a thread: x, the weight and the gate are requested together before the
+// row's sum is formed, and x stays in registers.
+__global__ void norm_gate_vec2_kernel(const float* __restrict__ x, long x_stride, const float* __restrict__ w,
+                                      const __nv_bfloat16* __restrict__ g, long g_stride, __nv_bfloat16* __restrict__ out,
+                                      long out_stride, int d, float eps, float mult) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float4* xr = reinterpret_cast<const float4*>(x + (long)blockIdx.x * x_stride);
+    const float4* wr = reinterpret_cast<const float4*>(w);
+    const int d4 = d >> 2;
+    float4 xv[2], wv[2];
+    uint2 gv[2];
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int i = threadIdx.x + u * blockDim.x;
+        xv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        wv[u] = xv[u];
+        gv[u] = make_uint2(0u, 0u);
+        if (i < d4) {
+            xv[u] = xr[i];
+            wv[u] = wr[i];
+            if (g != nullptr) gv[u] = *reinterpret_cast<const uint2*>(g + (long)blockIdx.x * g_stride + i * 4);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        ss = fmaf(xv[u].x, xv[u].x, ss); ss = fmaf(xv[u].y, xv[u].y, ss);
+        ss = fmaf(xv[u].z, xv[u].z, ss); ss = fmaf(xv[u].w, xv[u].w, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)d + eps);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int i = threadIdx.x + u * blockDim.x;
+        if (i >= d4) continue;
+        float y[4] = {(xv[u].x * inv) * wv[u].x, (xv[u].y * inv) * wv[u].y, (xv[u].z * inv) * wv[u].z, (xv[u].w * inv) * wv[u].w};
+        if (g != nullptr) {
+            const float2 g0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv[u].x));
+            const float2 g1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gv[u].y));
+            y[0] *= 1.0f / (1.0f + expf(-g0.x)); y[1] *= 1.0f / (1.0f + expf(-g0.y));
+            y[2] *= 1.0f / (1.0f + expf(-g1.x)); y[3] *= 1.0f / (1.0f + expf(-g1.y));
+        }
+        __nv_bfloat162 o0 = __floats2bfloat162_rn(y[0] * mult, y[1] * mult), o1 = __floats2bfloat162_rn(y[2] * mult, y[3] * mult);
+        uint2 ov;
+        ov.x = *reinterpret_cast<uint32_t*>(&o0);
+        ov.y = *reinterpret_cast<uint32_t*>(&o1);
+        *reinterpret_cast<uint2*>(out + (long)blockIdx.x * out_stride + i * 4) = ov;
     }
 }
 
@@ -722,6 +830,11 @@ ZLM_EXPORT int zlm_gate_heads(const void* a, long a_stride, const void* g, long 
     if (dtype == ZLM_F32)
         e = launch_pdl(gate_heads_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)a, a_stride,
                        (const float*)g, g_stride, (float*)out, out_stride, total, heads, n, mult);
+    else if (dtype == ZLM_BF16 && n % 8 == 0 && a_stride % 8 == 0 && out_stride % 8 == 0 && (uintptr_t)a % 16 == 0 &&
+             (uintptr_t)out % 16 == 0)
+        e = launch_pdl(gate_heads_vec_kernel, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, stream,
+                       (const __nv_bfloat16*)a, a_stride, (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride,
+                       total / 8, heads * n / 8, n / 8, mult);
     else if (dtype == ZLM_BF16)
         e = launch_pdl(gate_heads_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)a, a_stride,
                        (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride, total, heads, n, mult);
@@ -740,6 +853,14 @@ ZLM_EXPORT int zlm_norm_gate(const float* x, long x_stride, const float* w, cons
     if (dtype == ZLM_F32)
         e = launch_pdl(norm_gate_kernel<float>, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, w, (const float*)g,
                        g_stride, (float*)out, out_stride, d, eps, mult);
+    else if (dtype == ZLM_BF16 && d % 4 == 0 && x_stride % 4 == 0 && g_stride % 4 == 0 && out_stride % 4 == 0 &&
+             (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)g % 8 == 0 && (uintptr_t)out % 8 == 0)
+        e = d <= 4096
+                ? launch_pdl(norm_gate_vec2_kernel, dim3(n_rows), dim3(min(512, max(32, ((d / 4 + 1) / 2 + 31) / 32 * 32))), 0,
+                             stream, x, x_stride, w, (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride, d, eps,
+                             mult)
+                : launch_pdl(norm_gate_vec_kernel, dim3(n_rows), dim3(256), 0, stream, x, x_stride, w,
+                             (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride, d, eps, mult);
     else if (dtype == ZLM_BF16)
         e = launch_pdl(norm_gate_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, w,
                        (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride, d, eps, mult);

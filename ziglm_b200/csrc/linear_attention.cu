@@ -197,6 +197,204 @@ decayed_linear_attention_kernel(const T* __restrict__ proj, long row_stride, int
     }
 }
 
+
+// The same work for bf16 rows whose key size is a multiple of 32 up to 128 and whose offsets, strides and value size
+// are multiples of 8 elements.  q, k and v are read 16 bytes a thread, and the rows of the next chunk are requested
+// before the arithmetic on this one begins; the keys are kept both ways round (transposed for the scores, as rows for
+// the state, where a thread then reads four key dimensions in one instruction); the decay of a value rides on the
+// multiplication that uses it.  With STATE_ONLY neither queries nor scores exist.
+static inline size_t la_fast_smem_floats(int D, bool state_only) {
+    size_t n = (size_t)LA_C * D + (size_t)LA_C * LA_VT + (size_t)D * LA_VT;                  // k_s, v_s, S_s
+    if (!state_only) n += (size_t)LA_C * D + (size_t)D * (LA_C + 1) + (size_t)LA_C * (LA_C + 1);   // q_s, kT_s, a_s
+    return n;
+}
+
+template <bool STATE_ONLY>
+__global__ void __launch_bounds__(LA_THREADS)
+la_fast_kernel(const __nv_bfloat16* __restrict__ proj, long row_stride, int q_off, int k_off, int v_off, int H, int D, int V,
+               int act, const float* __restrict__ pows, float* __restrict__ state, const int* __restrict__ slots,
+               const int* __restrict__ cu_seqlens, int n_seqs, float* __restrict__ seg_state, float* __restrict__ out,
+               long out_stride) {
+    extern __shared__ __align__(16) float la_smem[];
+    float* k_s = la_smem;                              // [C][D]
+    float* v_s = k_s + LA_C * D;                       // [C][VT]
+    float* S_s = v_s + LA_C * LA_VT;                   // [D][VT]
+    float* q_s = S_s + D * LA_VT;                      // [C][D]
+    float* kT_s = q_s + LA_C * D;                      // [D][C+1]
+    float* a_s = kT_s + D * (LA_C + 1);                // [C][C+1]
+    __shared__ float pw[LA_C + 1];
+
+    pdl_launch_dependents();
+    const int h = blockIdx.y, v0 = blockIdx.z * LA_VT;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nv = min(LA_VT, V - v0);                 // value columns of this tile (a multiple of 8)
+    for (int i = threadIdx.x; i <= LA_C; i += LA_THREADS) pw[i] = pows[h * (LA_C + 1) + i];
+    pdl_wait();
+    int b = blockIdx.x, seg = 0, n_segs = 1;
+    if (seg_state != nullptr && !la_find_segment(blockIdx.x, cu_seqlens, n_seqs, b, seg, n_segs)) return;
+    if (STATE_ONLY && seg == n_segs - 1) return;
+    int first = cu_seqlens[b], last = cu_seqlens[b + 1];
+    if (seg_state != nullptr) {
+        first += seg * LA_SEG;
+        last = min(last, first + LA_SEG);
+    }
+    const long hdv = (long)H * D * V;
+    float* st = state + (((long)slots[b] * H + h) * D) * V;
+    const float* from = seg == 0 ? st : seg_state + (long)(blockIdx.x - 1) * hdv + (long)h * D * V;
+    float* to = STATE_ONLY ? seg_state + (long)blockIdx.x * hdv + (long)h * D * V : st;
+    for (int i = threadIdx.x; i < D * LA_VT; i += LA_THREADS) {
+        const int d = i / LA_VT, v = i % LA_VT;
+        S_s[i] = (!STATE_ONLY && v < nv) ? from[(long)d * V + v0 + v] : 0.f;
+    }
+
+    // what a thread fetches of a chunk: two vectors of q and of k (the chunk holds C * D/8 <= 512), one of v
+    const int D8 = D >> 3;
+    int qj[2], qd[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const int idx = threadIdx.x + u * LA_THREADS;
+        qj[u] = idx < LA_C * D8 ? idx / D8 : -1;
+        qd[u] = (idx - (idx / D8) * D8) * 8;
+    }
+    const int vj = threadIdx.x < LA_C * (LA_VT / 8) ? threadIdx.x / (LA_VT / 8) : -1;
+    const int vd = (threadIdx.x % (LA_VT / 8)) * 8;
+    uint4 rq[2], rk[2], rv;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+    auto fetch = [&](int c0) {
+        const int n = min(LA_C, last - c0);
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            rq[u] = zero4; rk[u] = zero4;
+            if (qj[u] >= 0 && qj[u] < n) {
+                const __nv_bfloat16* row = proj + (long)(c0 + qj[u]) * row_stride + (long)h * D + qd[u];
+                if (!STATE_ONLY) rq[u] = *reinterpret_cast<const uint4*>(row + q_off);
+                rk[u] = *reinterpret_cast<const uint4*>(row + k_off);
+            }
+        }
+        rv = zero4;
+        if (vj >= 0 && vj < n && vd < nv)
+            rv = *reinterpret_cast<const uint4*>(proj + (long)(c0 + vj) * row_stride + v_off + (long)h * V + v0 + vd);
+    };
+    auto unpack = [&](const uint4& r, float* f) {
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 x = __bfloat1622float2(p[e]);
+            f[2 * e] = la_act(x.x, act);
+            f[2 * e + 1] = la_act(x.y, act);
+        }
+    };
+    auto stash = [&]() {
+        float f[8];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            if (qj[u] < 0) continue;
+            unpack(rk[u], f);
+            *reinterpret_cast<float4*>(k_s + qj[u] * D + qd[u]) = make_float4(f[0], f[1], f[2], f[3]);
+            *reinterpret_cast<float4*>(k_s + qj[u] * D + qd[u] + 4) = make_float4(f[4], f[5], f[6], f[7]);
+            if (!STATE_ONLY) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) kT_s[(qd[u] + e) * (LA_C + 1) + qj[u]] = f[e];
+                unpack(rq[u], f);
+                *reinterpret_cast<float4*>(q_s + qj[u] * D + qd[u]) = make_float4(f[0], f[1], f[2], f[3]);
+                *reinterpret_cast<float4*>(q_s + qj[u] * D + qd[u] + 4) = make_float4(f[4], f[5], f[6], f[7]);
+            }
+        }
+        if (vj >= 0) {
+            unpack(rv, f);
+            *reinterpret_cast<float4*>(v_s + vj * LA_VT + vd) = make_float4(f[0], f[1], f[2], f[3]);
+            *reinterpret_cast<float4*>(v_s + vj * LA_VT + vd + 4) = make_float4(f[4], f[5], f[6], f[7]);
+        }
+    };
+
+    if (first < last) fetch(first);
+    const int rpw = D >> 3;                            // key dimensions of a warp in the state update: 4, 8, 12 or 16
+    for (int c0 = first; c0 < last; c0 += LA_C) {
+        const int n = min(LA_C, last - c0);
+        __syncthreads();                               // the chunk before is done with the rows; its state is written
+        stash();
+        if (c0 + LA_C < last) fetch(c0 + LA_C);
+        __syncthreads();
+        if (!STATE_ONLY) {
+            // scores with their decay: a_s[i][j] = a^(i-j) (q_i . k_j) for j <= i.  A thread: rows warp, warp+8, .., column lane.
+            float s[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int d = 0; d < D; d += 4) {
+                const float k0 = kT_s[(d + 0) * (LA_C + 1) + lane], k1 = kT_s[(d + 1) * (LA_C + 1) + lane];
+                const float k2 = kT_s[(d + 2) * (LA_C + 1) + lane], k3 = kT_s[(d + 3) * (LA_C + 1) + lane];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const float4 qv = *reinterpret_cast<const float4*>(q_s + (warp + LA_WARPS * r) * D + d);
+                    s[r] = fmaf(qv.x, k0, s[r]); s[r] = fmaf(qv.y, k1, s[r]);
+                    s[r] = fmaf(qv.z, k2, s[r]); s[r] = fmaf(qv.w, k3, s[r]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int i = warp + LA_WARPS * r;
+                a_s[i * (LA_C + 1) + lane] = lane <= i ? s[r] * pw[i - lane] : 0.f;
+            }
+            __syncthreads();
+            // outputs: o_i = sum_j a_s[i][j] v_j + a^(i+1) S^T q_i.  A thread: rows warp, warp+8, .., value column lane.
+            float o[4] = {0.f, 0.f, 0.f, 0.f}, p[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < n; ++j) {
+                const float vv = v_s[j * LA_VT + lane];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) o[r] = fmaf(a_s[(warp + LA_WARPS * r) * (LA_C + 1) + j], vv, o[r]);
+            }
+            for (int d = 0; d < D; d += 4) {
+                const float s0 = S_s[(d + 0) * LA_VT + lane], s1 = S_s[(d + 1) * LA_VT + lane];
+                const float s2 = S_s[(d + 2) * LA_VT + lane], s3 = S_s[(d + 3) * LA_VT + lane];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const float4 qv = *reinterpret_cast<const float4*>(q_s + (warp + LA_WARPS * r) * D + d);
+                    p[r] = fmaf(qv.x, s0, p[r]); p[r] = fmaf(qv.y, s1, p[r]);
+                    p[r] = fmaf(qv.z, s2, p[r]); p[r] = fmaf(qv.w, s3, p[r]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int i = warp + LA_WARPS * r;
+                if (i < n && lane < nv)
+                    out[(long)(c0 + i) * out_stride + (long)h * V + v0 + lane] = fmaf(pw[i + 1], p[r], o[r]);
+            }
+            __syncthreads();                           // everyone has read the old state
+        }
+        // S' = a^n S + sum_j k_j (v_j a^(n-1-j))^T.  A thread: key dimensions warp * rpw .. + rpw, value column lane.
+        {
+            const float an = pw[n];
+            const int dbase = warp * rpw;
+            for (int g = 0; g < rpw; g += 8) {
+                const bool two = g + 4 < rpw;
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (int j = 0; j < n; ++j) {
+                    const float vw = v_s[j * LA_VT + lane] * pw[n - 1 - j];
+                    const float4 ka = *reinterpret_cast<const float4*>(k_s + j * D + dbase + g);
+                    acc[0] = fmaf(ka.x, vw, acc[0]); acc[1] = fmaf(ka.y, vw, acc[1]);
+                    acc[2] = fmaf(ka.z, vw, acc[2]); acc[3] = fmaf(ka.w, vw, acc[3]);
+                    if (two) {
+                        const float4 kb = *reinterpret_cast<const float4*>(k_s + j * D + dbase + g + 4);
+                        acc[4] = fmaf(kb.x, vw, acc[4]); acc[5] = fmaf(kb.y, vw, acc[5]);
+                        acc[6] = fmaf(kb.z, vw, acc[6]); acc[7] = fmaf(kb.w, vw, acc[7]);
+                    }
+                }
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    if (r < 4 || two) {
+                        float* sp = S_s + (dbase + g + r) * LA_VT + lane;
+                        *sp = fmaf(an, *sp, acc[r]);
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    if (!STATE_ONLY && seg != n_segs - 1) return;      // the next segment starts from what the scan left it
+    for (int i = threadIdx.x; i < D * LA_VT; i += LA_THREADS) {
+        const int d = i / LA_VT, v = i % LA_VT;
+        if (v < nv) to[(long)d * V + v0 + v] = S_s[i];
+    }
+}
+
 // Step 2: seg_state[g] holds the local sum of segment g (entries of last segments are unused).  Afterwards entry g
 // holds the state segment g + 1 starts from.  One thread an element of [D, V], one block row a (sequence, head).
 __global__ void __launch_bounds__(256)
@@ -240,9 +438,33 @@ static int la_launch(const T* proj, long row_stride, int q_off, int k_off, int v
     const int Dp = (D + 3) / 4 * 4;
     const size_t smem = la_smem_floats(Dp) * sizeof(float);
     const int v_tiles = (V + LA_VT - 1) / LA_VT;
+    cudaError_t e;
+    if (sizeof(T) == 2 && D % 32 == 0 && D <= 128 && V % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 &&
+        row_stride % 8 == 0 && (uintptr_t)proj % 16 == 0) {
+        const __nv_bfloat16* rows = reinterpret_cast<const __nv_bfloat16*>(proj);
+        const size_t smem_full = la_fast_smem_floats(D, false) * sizeof(float), smem_local = la_fast_smem_floats(D, true) * sizeof(float);
+        auto full = la_fast_kernel<false>;
+        auto local = la_fast_kernel<true>;
+        if ((e = cudaFuncSetAttribute(full, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_full)) != cudaSuccess) return (int)e;
+        if (seg_state == nullptr) {
+            e = launch_pdl(full, dim3(n_seqs, H, v_tiles), dim3(LA_THREADS), smem_full, stream, rows, row_stride, q_off, k_off,
+                           v_off, H, D, V, act, pows, state, slots, cu_seqlens, n_seqs, (float*)nullptr, out, out_stride);
+            return e == cudaSuccess ? launch_status() : (int)e;
+        }
+        if ((e = cudaFuncSetAttribute(local, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_local)) != cudaSuccess) return (int)e;
+        dim3 grid(n_segments, H, v_tiles);
+        e = launch_pdl(local, grid, dim3(LA_THREADS), smem_local, stream, rows, row_stride, q_off, k_off, v_off, H, D, V, act,
+                       pows, state, slots, cu_seqlens, n_seqs, seg_state, out, out_stride);
+        if (e != cudaSuccess) return (int)e;
+        e = launch_pdl(la_segment_scan_kernel, dim3(n_seqs, H, (D * V + 255) / 256), dim3(256), 0, stream, pows,
+                       (const float*)state, slots, cu_seqlens, n_seqs, H, D * V, seg_state);
+        if (e != cudaSuccess) return (int)e;
+        e = launch_pdl(full, grid, dim3(LA_THREADS), smem_full, stream, rows, row_stride, q_off, k_off, v_off, H, D, V, act, pows,
+                       state, slots, cu_seqlens, n_seqs, seg_state, out, out_stride);
+        return e == cudaSuccess ? launch_status() : (int)e;
+    }
     auto full = decayed_linear_attention_kernel<T, false>;
     auto local = decayed_linear_attention_kernel<T, true>;
-    cudaError_t e;
     if (smem > 48 * 1024) {
         if ((e = cudaFuncSetAttribute(full, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
         if ((e = cudaFuncSetAttribute(local, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;

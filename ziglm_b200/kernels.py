@@ -117,9 +117,9 @@ _PROTOTYPES = {
         "zlm_attention_general_scratch": [c_int, c_int, c_int, c_int, c_int],
     },
     "attention_tc": {
-        "zlm_attention_decode": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p,
-                                 c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p,
-                                 c_void_p, c_void_p],
+        "zlm_attention_decode": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int,
+                                 c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int,
+                                 c_void_p, c_void_p, c_void_p],
         "zlm_attention_decode_flat": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p,
                                       c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p,
                                       c_void_p, c_long, c_int, c_int, c_int, c_void_p, c_void_p, c_long, c_void_p],
@@ -871,8 +871,10 @@ def _tc_attention_ok(dtype: torch.dtype, n_heads: int, n_kv: int, head_dim: int,
 def attention_decode(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
                      window: Optional[int], positions: torch.Tensor, seq_of_token: torch.Tensor,
                      block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_size: int,
-                     n_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor, softcap: float = 0.0) -> bool:
-    """Tensor-core attention for steps of one token per sequence (bf16, head size 64 or 128).
+                     n_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor, softcap: float = 0.0,
+                     keep_first: int = 0, sinks: Optional[torch.Tensor] = None) -> bool:
+    """Tensor-core attention for steps of one token per sequence (bf16, head size 64 or 128); ``keep_first`` and
+    ``sinks`` as :func:`attention_general` takes them.
 
     Each token's query heads are grouped by key/value head so that the cache is read once per group; the keys
     of a sequence are split over ``n_splits`` blocks whose partial results go through the float32 scratch
@@ -891,9 +893,13 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: i
         raise KernelError("attention_decode: cache pages must be [n_pages, n_kv, page_size, head_dim]")
     if part_o.numel() < T * n_heads * n_splits * head_dim or part_ml.numel() < T * n_heads * n_splits * 2:
         raise KernelError("attention_decode: the scratch is too small for this many splits")
+    if sinks is not None:
+        _cuda(sinks, "sinks", torch.float32)
+        if sinks.numel() != n_heads or not sinks.is_contiguous():
+            raise KernelError("attention_decode: one sink per query head is needed")
     status = _fn("attention_tc", "zlm_attention_decode")(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, n_heads, n_kv, head_dim, scale, float(softcap or 0.0),
-        int(window or 0),
+        int(window or 0), int(keep_first or 0) if window else 0, _ptr(sinks),
         positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0),
         k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, n_splits, part_o.data_ptr(),
         part_ml.data_ptr(), _stream())
@@ -1109,13 +1115,23 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
     (the caller multiplies when it was not: in a prompt one pass of ``sigmoid_mul`` over coalesced rows costs less
     than the same work in the prompt kernel's epilogue, where every thread walks a row of its own)."""
     keep_first = int(keep_first or 0) if window else 0
-    # kept first tokens and sinks: the tcgen05 prompt kernel knows both, the other tensor-core kernels neither
+    # kept first tokens and sinks: the tcgen05 prompt kernel and the decode kernel that splits a sequence's keys
+    # know both, the other tensor-core kernels neither
     plain_only = keep_first > 0 or sinks is not None
-    if plain_only and not step.single_token and step.max_new >= 16 and _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim,
-                                                                                        io.page_size):
-        if attention_prefill_fmha(qkv, out, step.n_seqs, step.max_new, n_heads, n_kv, head_dim, scale, window,
-                                  step.cu_seqlens, step.past_lens, io.block_table, io.k_pages, io.v_pages, io.page_size,
-                                  softcap=softcap, keep_first=keep_first, sinks=sinks):
+    if plain_only and _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
+        if step.single_token:
+            n_splits = decode_splits(step.n_tokens, n_kv, min(step.max_total, window + keep_first) if window else step.max_total,
+                                     io.page_size)
+            part_o = step.ws.buf("attn_part_o", (step.n_tokens * n_heads * n_splits * head_dim,), torch.float32)
+            part_ml = step.ws.buf("attn_part_ml", (step.n_tokens * n_heads * n_splits * 2,), torch.float32)
+            if attention_decode(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions, step.seq_of_token,
+                                io.block_table, io.k_pages, io.v_pages, io.page_size, n_splits, part_o, part_ml,
+                                softcap=softcap, keep_first=keep_first, sinks=sinks):
+                return False
+        elif step.max_new >= 16 and attention_prefill_fmha(
+                qkv, out, step.n_seqs, step.max_new, n_heads, n_kv, head_dim, scale, window, step.cu_seqlens,
+                step.past_lens, io.block_table, io.k_pages, io.v_pages, io.page_size, softcap=softcap,
+                keep_first=keep_first, sinks=sinks):
             return False
     if not plain_only and _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
         n_blocks = attention_decode_flat_blocks(step.n_tokens, n_heads, n_kv, head_dim) if step.single_token else 0
@@ -1157,7 +1173,7 @@ def fast_attention_libraries(dtype: torch.dtype, head_dim: int, n_heads: int = 1
     """The sources of the tensor-core attention kernels if they take this shape and these options, else nothing (the
     plain kernel runs)."""
     if keep_first or sinks:
-        return ("attention_fmha",) if _tc_attention_ok(dtype, n_heads, n_kv, head_dim, 64) else ()
+        return ("attention_tc", "attention_fmha") if _tc_attention_ok(dtype, n_heads, n_kv, head_dim, 64) else ()
     return ("attention_tc", "attention_fmha") if _tc_attention_ok(dtype, n_heads, n_kv, head_dim, 64) else ()
 
 
