@@ -29,7 +29,8 @@ def _tol(dtype, f32=(1e-5, 1e-5), bf16=(2e-2, 2e-2)):
 
 @pytest.mark.parametrize("dtype", TYPES)
 @pytest.mark.parametrize("H,G,D,V,rot,whole,mix", [(6, 2, 24, 40, 16, True, 2), (4, 4, 64, 64, 64, True, 1),
-                                                    (5, 1, 16, 8, 2, False, 2), (2, 1, 128, 128, 64, True, 0)])
+                                                    (5, 1, 16, 8, 2, False, 2), (2, 1, 128, 128, 64, True, 0),
+                                                    (3, 1, 32, 16, 16, False, 1), (8, 2, 64, 64, 32, False, 2)])
 def test_norm_of_whole_q_and_k_rotation_of_adjacent_pairs_mixed_values_and_cache_write(dtype, H, G, D, V, rot, whole, mix):
     """Two sequences (a prompt of 70 after 3 cached tokens, one decoded token at position 130) with shuffled pages; heads
     kept with zeros behind them; rows wider than the heads.  The plain side turns adjacent pairs of the heads as the
@@ -208,7 +209,8 @@ def _lin_step(slots, new):
 
 @pytest.mark.parametrize("dtype", TYPES)
 @pytest.mark.parametrize("H,D,V,decay", [(3, 12, 20, [0.5, 0.9, 1.0]), (2, 64, 64, [0.999, 0.97]), (1, 5, 3, [1.0]),
-                                          (2, 33, 35, [0.3, 0.95]), (4, 128, 32, [0.6, 0.88, 0.97, 0.999])])
+                                          (2, 33, 35, [0.3, 0.95]), (4, 128, 32, [0.6, 0.88, 0.97, 0.999]),
+                                          (1, 160, 40, [0.9])])
 def test_decayed_linear_attention_over_steps_with_slots_used_again(dtype, H, D, V, decay):
     """Three sequences in slots 2, 0, 3 of a state that holds garbage elsewhere: a prompt each (1, 70 and 131 tokens),
     a step of 2, 33 and 1 tokens, then single tokens; against the recurrence token by token.  The rows are wider than

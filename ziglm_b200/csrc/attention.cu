@@ -793,6 +793,161 @@ qk_prep_kernel(T* __restrict__ qkv, long row_stride, int n_heads, int n_kv, int 
     }
 }
 
+
+__device__ __forceinline__ void bf16x8_to_float(const uint4& v, float (&f)[8]) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 x = __bfloat1622float2(p[k]);
+        f[2 * k] = x.x;
+        f[2 * k + 1] = x.y;
+    }
+}
+
+__device__ __forceinline__ uint4 float_to_bf16x8(const float (&f)[8]) {
+    uint4 v;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) p[k] = __halves2bfloat162(__float2bfloat16_rn(f[2 * k]), __float2bfloat16_rn(f[2 * k + 1]));
+    return v;
+}
+
+__device__ __forceinline__ void load_float8(const float* __restrict__ p, float (&f)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// The same for bf16 rows whose heads, halves, value sizes and strides are multiples of 8 elements: 16 bytes a thread
+// and turn.  q and k of the token are read once, into shared memory (q_len + k_len elements), while their squares are
+// summed; the second pass works from there.  Same arithmetic, element by element.
+__global__ void __launch_bounds__(256)
+qk_prep_vec_kernel(__nv_bfloat16* __restrict__ qkv, long row_stride, int n_heads, int n_kv, int hd, int rot,
+                   const float* __restrict__ inv_freq, const float* __restrict__ q_w, const float* __restrict__ k_w,
+                   int n_q, int n_k, float norm_eps, int mix_mode, float mix, __nv_bfloat16* __restrict__ mix_buf,
+                   int v_dim, const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                   const int* __restrict__ block_table, int bt_stride, __nv_bfloat16* __restrict__ k_pages,
+                   __nv_bfloat16* __restrict__ v_pages, int page_size, long page_stride) {
+    extern __shared__ uint4 row_s[];
+    __shared__ float cos_s[ROPE_MAX_HALF], sin_s[ROPE_MAX_HALF];
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int pos = positions[t];                       // positions, tables and frequencies are older than the step
+    const int half = rot / 2;
+    const bool turn = inv_freq != nullptr && half > 0;
+    if (turn)
+        for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sin_s[i], &cos_s[i]);
+    __nv_bfloat16* kdst = nullptr;
+    __nv_bfloat16* vdst = nullptr;
+    if (k_pages != nullptr) {
+        const int b = seq_of_token[t];
+        const int page = block_table[(long)b * bt_stride + pos / page_size];
+        const long off = (long)page * page_stride + (long)(pos % page_size) * hd;
+        kdst = k_pages + off;
+        vdst = v_pages + off;
+    }
+    pdl_wait();
+    __nv_bfloat16* row0 = qkv + (long)t * row_stride;
+    const int q_len = n_heads * hd, k_len = n_kv * hd;
+    const int q_units = q_len / 8, qk_units = (q_len + k_len) / 8;
+    float ssq = 0.f, ssk = 0.f;
+    for (int u = threadIdx.x; u < qk_units; u += blockDim.x) {
+        const uint4 v = *reinterpret_cast<const uint4*>(row0 + (long)u * 8);
+        row_s[u] = v;
+        float f[8];
+        bf16x8_to_float(v, f);
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss = fmaf(f[k], f[k], ss);
+        if (u < q_units) ssq += ss; else ssk += ss;
+    }
+    float inv_q = 1.0f, inv_k = 1.0f;
+    if (q_w != nullptr) inv_q = 1.0f / sqrtf(block_sum(ssq, scratch) / (float)n_q + norm_eps);
+    if (k_w != nullptr) inv_k = 1.0f / sqrtf(block_sum(ssk, scratch) / (float)n_k + norm_eps);
+    __syncthreads();
+    const long kv_head_stride = (long)page_size * hd;
+    const int qk_heads = n_heads + n_kv;
+    if (turn) {
+        const int units = half / 8;
+        for (int idx = threadIdx.x; idx < qk_heads * units; idx += blockDim.x) {
+            const int head = idx / units, i0 = (idx - head * units) * 8;
+            const bool is_k = head >= n_heads;
+            const int at = head * hd + i0;
+            float a[8], b2[8];
+            bf16x8_to_float(row_s[at / 8], a);
+            bf16x8_to_float(row_s[(at + half) / 8], b2);
+            const float* w = is_k ? k_w : q_w;
+            if (w != nullptr) {
+                const int wi = at - (is_k ? q_len : 0);
+                const float inv = is_k ? inv_k : inv_q;
+                float wa[8], wb[8];
+                load_float8(w + wi, wa);
+                load_float8(w + wi + half, wb);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    a[k] = (a[k] * inv) * wa[k];
+                    b2[k] = (b2[k] * inv) * wb[k];
+                }
+            }
+            float lo[8], hi[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float c = cos_s[i0 + k], sn = sin_s[i0 + k];
+                lo[k] = a[k] * c - b2[k] * sn;
+                hi[k] = b2[k] * c + a[k] * sn;
+            }
+            const uint4 lo_v = float_to_bf16x8(lo), hi_v = float_to_bf16x8(hi);
+            *reinterpret_cast<uint4*>(row0 + at) = lo_v;
+            *reinterpret_cast<uint4*>(row0 + at + half) = hi_v;
+            if (kdst && is_k) {
+                __nv_bfloat16* d = kdst + (long)(head - n_heads) * kv_head_stride;
+                *reinterpret_cast<uint4*>(d + i0) = lo_v;
+                *reinterpret_cast<uint4*>(d + i0 + half) = hi_v;
+            }
+        }
+    }
+    const int first_rest = turn ? rot : 0, rest_units = (hd - first_rest) / 8;
+    for (int idx = threadIdx.x; idx < qk_heads * rest_units; idx += blockDim.x) {
+        const int head = idx / rest_units, i0 = first_rest + (idx - head * rest_units) * 8;
+        const bool is_k = head >= n_heads;
+        const float* w = is_k ? k_w : q_w;
+        if (w == nullptr && !(kdst && is_k)) continue;      // nothing changes and nothing is stored
+        const int at = head * hd + i0;
+        uint4 o = row_s[at / 8];
+        if (w != nullptr) {
+            const float inv = is_k ? inv_k : inv_q;
+            float a[8], wa[8];
+            bf16x8_to_float(o, a);
+            load_float8(w + at - (is_k ? q_len : 0), wa);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) a[k] = (a[k] * inv) * wa[k];
+            o = float_to_bf16x8(a);
+            *reinterpret_cast<uint4*>(row0 + at) = o;
+        }
+        if (kdst && is_k) *reinterpret_cast<uint4*>(kdst + (long)(head - n_heads) * kv_head_stride + i0) = o;
+    }
+    __nv_bfloat16* vrow = row0 + q_len + k_len;
+    const int v_units = hd / 8;
+    for (int idx = threadIdx.x; idx < n_kv * v_units; idx += blockDim.x) {
+        const int g = idx / v_units, i0 = (idx - g * v_units) * 8;
+        uint4 o = *reinterpret_cast<const uint4*>(vrow + g * hd + i0);
+        if (mix_mode != 0 && i0 < v_dim) {                   // what lies behind a head's v_dim values is zero and stays
+            __nv_bfloat16* other = mix_buf + ((long)t * n_kv + g) * v_dim + i0;
+            if (mix_mode == 1) *reinterpret_cast<uint4*>(other) = o;
+            else {
+                float a[8], m[8];
+                bf16x8_to_float(o, a);
+                bf16x8_to_float(*reinterpret_cast<const uint4*>(other), m);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) a[k] = (1.0f - mix) * a[k] + mix * m[k];
+                o = float_to_bf16x8(a);
+                *reinterpret_cast<uint4*>(vrow + g * hd + i0) = o;
+            }
+        }
+        if (vdst) *reinterpret_cast<uint4*>(vdst + (long)g * kv_head_stride + i0) = o;
+    }
+}
+
 }  // namespace zlm
 
 using namespace zlm;
@@ -954,6 +1109,15 @@ ZLM_EXPORT int zlm_qk_prep(void* qkv, int dtype, long row_stride, int T, int n_h
         e = launch_pdl(qk_prep_kernel<float>, dim3(T), dim3(threads), 0, stream, (float*)qkv, row_stride, n_heads, n_kv, hd,
                        rot, inv_freq, q_w, k_w, n_q, n_k, norm_eps, mix_mode, mix, (float*)mix_buf, v_dim, positions, seq_of_token,
                        block_table, bt_stride, (float*)k_pages, (float*)v_pages, page_size, page_stride);
+    else if (dtype == ZLM_BF16 && hd % 8 == 0 && rot % 16 == 0 && row_stride % 8 == 0 && page_stride % 8 == 0 &&
+             (mix_mode == 0 || v_dim % 8 == 0) && (uintptr_t)qkv % 16 == 0 && (uintptr_t)k_pages % 16 == 0 &&
+             (uintptr_t)v_pages % 16 == 0 && (uintptr_t)mix_buf % 16 == 0 && (uintptr_t)q_w % 16 == 0 &&
+             (uintptr_t)k_w % 16 == 0 && (size_t)(n_heads + n_kv) * hd * 2 <= 40 * 1024)
+        e = launch_pdl(qk_prep_vec_kernel, dim3(T), dim3(work >= 256 * 8 ? 256 : (work >= 128 * 8 ? 128 : 64)),
+                       (size_t)(n_heads + n_kv) * hd * 2, stream, (__nv_bfloat16*)qkv, row_stride, n_heads, n_kv, hd, rot,
+                       inv_freq, q_w, k_w, n_q, n_k, norm_eps, mix_mode, mix, (__nv_bfloat16*)mix_buf, v_dim, positions,
+                       seq_of_token, block_table, bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size,
+                       page_stride);
     else if (dtype == ZLM_BF16)
         e = launch_pdl(qk_prep_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, (__nv_bfloat16*)qkv, row_stride,
                        n_heads, n_kv, hd, rot, inv_freq, q_w, k_w, n_q, n_k, norm_eps, mix_mode, mix, (__nv_bfloat16*)mix_buf,

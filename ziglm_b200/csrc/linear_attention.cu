@@ -419,6 +419,69 @@ la_segment_scan_kernel(const float* __restrict__ pows, const float* __restrict__
     }
 }
 
+
+// A step in which every sequence brings one token: S' = a S + k v^T and o = S'^T q straight on the state in global
+// memory.  A block owns a (sequence, head, tile of 32 value columns); lane l owns column l, warp w the key dimensions
+// w, w + 8, ...  The state's elements are requested before q and k are in shared memory, a batch of
+// LA_DEC_ROWS key dimensions a thread at a time; the warps' partial outputs are summed in a fixed order.
+constexpr int LA_DEC_ROWS = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(LA_THREADS)
+la_decode_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_off, int v_off, int H, int D, int V, int act,
+                 const float* __restrict__ pows, float* __restrict__ state, const int* __restrict__ slots,
+                 const int* __restrict__ cu_seqlens, float* __restrict__ out, long out_stride) {
+    __shared__ float q_s[LA_MAX_D], k_s[LA_MAX_D], red[LA_WARPS][LA_VT];
+    pdl_launch_dependents();
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int v = blockIdx.z * LA_VT + lane;
+    const float a = pows[h * (LA_C + 1) + 1];
+    pdl_wait();
+    float* st = state + (((long)slots[b] * H + h) * D) * V + v;
+    float s_reg[LA_DEC_ROWS];
+#pragma unroll
+    for (int u = 0; u < LA_DEC_ROWS; ++u) {
+        const int d = warp + u * LA_WARPS;
+        s_reg[u] = (v < V && d < D) ? st[(long)d * V] : 0.f;
+    }
+    const long t = cu_seqlens[b];
+    const T* row = proj + t * row_stride;
+    for (int i = threadIdx.x; i < D; i += LA_THREADS) {
+        q_s[i] = la_act(to_float(row[q_off + h * D + i]), act);
+        k_s[i] = la_act(to_float(row[k_off + h * D + i]), act);
+    }
+    const float vv = v < V ? la_act(to_float(row[v_off + h * V + v]), act) : 0.f;
+    __syncthreads();
+    float acc = 0.f;
+    for (int base = 0; base < D; base += LA_DEC_ROWS * LA_WARPS) {
+        if (base > 0) {
+#pragma unroll
+            for (int u = 0; u < LA_DEC_ROWS; ++u) {
+                const int d = base + warp + u * LA_WARPS;
+                s_reg[u] = (v < V && d < D) ? st[(long)d * V] : 0.f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < LA_DEC_ROWS; ++u) {
+            const int d = base + warp + u * LA_WARPS;
+            if (v < V && d < D) {
+                const float s = fmaf(a, s_reg[u], k_s[d] * vv);
+                st[(long)d * V] = s;
+                acc = fmaf(s, q_s[d], acc);
+            }
+        }
+    }
+    red[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && v < V) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < LA_WARPS; ++w) o += red[w][lane];
+        out[t * out_stride + h * V + v] = o;
+    }
+}
+
 }  // namespace zlm
 
 using namespace zlm;
@@ -430,15 +493,21 @@ ZLM_EXPORT int zlm_linear_attention_chunk() { return LA_C; }
 // its value at v_off + h*V.  act 0: as they are, 1: through silu.  pows: float [H][chunk + 1] with decay_h^n.
 // state: float [n_slots][H][D][V]; slots, cu_seqlens: the step's sequences.  out: float rows [T][out_stride].
 // seg_state: null, or float [zlm_linear_attention_segments(T, n_seqs)][H][D][V] of scratch, with which the step's T
-// tokens run as segments side by side (three launches instead of one).
+// tokens run as segments side by side (three launches instead of one).  single_token: every sequence brings exactly
+// one token (the state is updated in place, without chunks).
 template <typename T>
 static int la_launch(const T* proj, long row_stride, int q_off, int k_off, int v_off, int H, int D, int V, int act,
                      const float* pows, float* state, const int* slots, const int* cu_seqlens, int n_seqs,
-                     int n_segments, float* seg_state, float* out, long out_stride, cudaStream_t stream) {
+                     int n_segments, bool single_token, float* seg_state, float* out, long out_stride, cudaStream_t stream) {
     const int Dp = (D + 3) / 4 * 4;
     const size_t smem = la_smem_floats(Dp) * sizeof(float);
     const int v_tiles = (V + LA_VT - 1) / LA_VT;
     cudaError_t e;
+    if (single_token) {
+        e = launch_pdl(la_decode_kernel<T>, dim3(n_seqs, H, v_tiles), dim3(LA_THREADS), 0, stream, proj, row_stride, q_off,
+                       k_off, v_off, H, D, V, act, pows, state, slots, cu_seqlens, out, out_stride);
+        return e == cudaSuccess ? launch_status() : (int)e;
+    }
     if (sizeof(T) == 2 && D % 32 == 0 && D <= 128 && V % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 &&
         row_stride % 8 == 0 && (uintptr_t)proj % 16 == 0) {
         const __nv_bfloat16* rows = reinterpret_cast<const __nv_bfloat16*>(proj);
@@ -493,16 +562,17 @@ ZLM_EXPORT int zlm_linear_attention_segment() { return LA_SEG; }
 ZLM_EXPORT int zlm_decayed_linear_attention(const void* proj, int dtype, long row_stride, int q_off, int k_off, int v_off,
                                             int H, int D, int V, int act, const float* pows, float* state,
                                             const int* slots, const int* cu_seqlens, int n_seqs, int n_tokens,
-                                            float* seg_state, float* out, long out_stride, cudaStream_t stream) {
+                                            int single_token, float* seg_state, float* out, long out_stride,
+                                            cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (H <= 0 || D <= 0 || V <= 0 || (act != 0 && act != 1)) return ZLM_ERR_BAD_ARG;
     if (D > LA_MAX_D || H > 65535 || (V + LA_VT - 1) / LA_VT > 65535 || n_seqs > 65535) return ZLM_ERR_UNSUPPORTED;
     const int n_segments = zlm_linear_attention_segments(n_tokens, n_seqs);
     if (dtype == ZLM_F32)
         return la_launch((const float*)proj, row_stride, q_off, k_off, v_off, H, D, V, act, pows, state, slots, cu_seqlens,
-                         n_seqs, n_segments, seg_state, out, out_stride, stream);
+                         n_seqs, n_segments, single_token != 0, seg_state, out, out_stride, stream);
     if (dtype == ZLM_BF16)
         return la_launch((const __nv_bfloat16*)proj, row_stride, q_off, k_off, v_off, H, D, V, act, pows, state, slots,
-                         cu_seqlens, n_seqs, n_segments, seg_state, out, out_stride, stream);
+                         cu_seqlens, n_seqs, n_segments, single_token != 0, seg_state, out, out_stride, stream);
     return ZLM_ERR_UNSUPPORTED;
 }

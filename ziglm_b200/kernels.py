@@ -86,7 +86,7 @@ _PROTOTYPES = {
         "zlm_linear_attention_segment": [],
         "zlm_linear_attention_segments": [c_int, c_int],
         "zlm_decayed_linear_attention": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_long, c_void_p],
+                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_long, c_void_p],
     },
     "moe": {
         "zlm_moe_route": [c_void_p, c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -789,7 +789,7 @@ def decayed_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: 
     columns q_off + h*dim, k_off + h*dim, v_off + h*value_dim of ``proj``'s rows, read through ``activation``
     (None or "silu").  ``pows`` float32 [n_heads, chunk + 1]: decay_h^n.  ``out`` float32 [T, n_heads * value_dim].
     A step with a sequence of more tokens than a segment runs its segments side by side, with their start states in
-    the step's scratch."""
+    the step's scratch; a step of one token a sequence updates the state in place."""
     _rows(proj, "proj"); _rows(out, "out"); _cuda(pows, "pows", torch.float32); _cuda(state, "state", torch.float32)
     T = proj.shape[0]
     if activation not in (None, "silu"):
@@ -810,7 +810,8 @@ def decayed_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: 
     _check(_fn("linear_attention", "zlm_decayed_linear_attention")(
         proj.data_ptr(), code(proj.dtype), _row_stride(proj), q_off, k_off, v_off, n_heads, dim, value_dim,
         1 if activation == "silu" else 0, pows.data_ptr(), state.data_ptr(), step.slots.data_ptr(),
-        step.cu_seqlens.data_ptr(), step.n_seqs, T, _ptr(seg_state), out.data_ptr(), _row_stride(out), _stream()),
+        step.cu_seqlens.data_ptr(), step.n_seqs, T, 1 if step.single_token and T == step.n_seqs else 0, _ptr(seg_state),
+        out.data_ptr(), _row_stride(out), _stream()),
         "decayed_linear_attention")
 
 
