@@ -200,28 +200,28 @@ decayed_linear_attention_kernel(const T* __restrict__ proj, long row_stride, int
 
 // The same work for bf16 rows whose key size is a multiple of 32 up to 128 and whose offsets, strides and value size
 // are multiples of 8 elements.  q, k and v are read 16 bytes a thread, and the rows of the next chunk are requested
-// before the arithmetic on this one begins; the keys are kept both ways round (transposed for the scores, as rows for
-// the state, where a thread then reads four key dimensions in one instruction); the decay of a value rides on the
-// multiplication that uses it.  With STATE_ONLY neither queries nor scores exist.
+// before the arithmetic on this one begins; a key is a row of D + 4 floats, so that a lane reads four dimensions of its
+// own key in one instruction without a bank conflict (the scores) and a warp four dimensions of one key as a broadcast
+// (the state); the decay of a value rides on the multiplication that uses it.  With STATE_ONLY neither queries nor scores exist.
 static inline size_t la_fast_smem_floats(int D, bool state_only) {
-    size_t n = (size_t)LA_C * D + (size_t)LA_C * LA_VT + (size_t)D * LA_VT;                  // k_s, v_s, S_s
-    if (!state_only) n += (size_t)LA_C * D + (size_t)D * (LA_C + 1) + (size_t)LA_C * (LA_C + 1);   // q_s, kT_s, a_s
+    size_t n = (size_t)LA_C * (D + 4) + (size_t)LA_C * LA_VT + (size_t)D * LA_VT;            // k_s, v_s, S_s
+    if (!state_only) n += (size_t)LA_C * D + (size_t)LA_C * (LA_C + 1);                       // q_s, a_s
     return n;
 }
 
 template <bool STATE_ONLY>
-__global__ void __launch_bounds__(LA_THREADS)
+__global__ void __launch_bounds__(LA_THREADS, 3)
 la_fast_kernel(const __nv_bfloat16* __restrict__ proj, long row_stride, int q_off, int k_off, int v_off, int H, int D, int V,
                int act, const float* __restrict__ pows, float* __restrict__ state, const int* __restrict__ slots,
                const int* __restrict__ cu_seqlens, int n_seqs, float* __restrict__ seg_state, float* __restrict__ out,
                long out_stride) {
     extern __shared__ __align__(16) float la_smem[];
-    float* k_s = la_smem;                              // [C][D]
-    float* v_s = k_s + LA_C * D;                       // [C][VT]
+    const int KS = D + 4;                              // floats of a key's row
+    float* k_s = la_smem;                              // [C][D + 4]
+    float* v_s = k_s + LA_C * KS;                      // [C][VT]
     float* S_s = v_s + LA_C * LA_VT;                   // [D][VT]
     float* q_s = S_s + D * LA_VT;                      // [C][D]
-    float* kT_s = q_s + LA_C * D;                      // [D][C+1]
-    float* a_s = kT_s + D * (LA_C + 1);                // [C][C+1]
+    float* a_s = q_s + LA_C * D;                       // [C][C+1]
     __shared__ float pw[LA_C + 1];
 
     pdl_launch_dependents();
@@ -290,11 +290,9 @@ la_fast_kernel(const __nv_bfloat16* __restrict__ proj, long row_stride, int q_of
         for (int u = 0; u < 2; ++u) {
             if (qj[u] < 0) continue;
             unpack(rk[u], f);
-            *reinterpret_cast<float4*>(k_s + qj[u] * D + qd[u]) = make_float4(f[0], f[1], f[2], f[3]);
-            *reinterpret_cast<float4*>(k_s + qj[u] * D + qd[u] + 4) = make_float4(f[4], f[5], f[6], f[7]);
+            *reinterpret_cast<float4*>(k_s + qj[u] * KS + qd[u]) = make_float4(f[0], f[1], f[2], f[3]);
+            *reinterpret_cast<float4*>(k_s + qj[u] * KS + qd[u] + 4) = make_float4(f[4], f[5], f[6], f[7]);
             if (!STATE_ONLY) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) kT_s[(qd[u] + e) * (LA_C + 1) + qj[u]] = f[e];
                 unpack(rq[u], f);
                 *reinterpret_cast<float4*>(q_s + qj[u] * D + qd[u]) = make_float4(f[0], f[1], f[2], f[3]);
                 *reinterpret_cast<float4*>(q_s + qj[u] * D + qd[u] + 4) = make_float4(f[4], f[5], f[6], f[7]);
@@ -319,13 +317,12 @@ la_fast_kernel(const __nv_bfloat16* __restrict__ proj, long row_stride, int q_of
             // scores with their decay: a_s[i][j] = a^(i-j) (q_i . k_j) for j <= i.  A thread: rows warp, warp+8, .., column lane.
             float s[4] = {0.f, 0.f, 0.f, 0.f};
             for (int d = 0; d < D; d += 4) {
-                const float k0 = kT_s[(d + 0) * (LA_C + 1) + lane], k1 = kT_s[(d + 1) * (LA_C + 1) + lane];
-                const float k2 = kT_s[(d + 2) * (LA_C + 1) + lane], k3 = kT_s[(d + 3) * (LA_C + 1) + lane];
+                const float4 kv = *reinterpret_cast<const float4*>(k_s + lane * KS + d);
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     const float4 qv = *reinterpret_cast<const float4*>(q_s + (warp + LA_WARPS * r) * D + d);
-                    s[r] = fmaf(qv.x, k0, s[r]); s[r] = fmaf(qv.y, k1, s[r]);
-                    s[r] = fmaf(qv.z, k2, s[r]); s[r] = fmaf(qv.w, k3, s[r]);
+                    s[r] = fmaf(qv.x, kv.x, s[r]); s[r] = fmaf(qv.y, kv.y, s[r]);
+                    s[r] = fmaf(qv.z, kv.z, s[r]); s[r] = fmaf(qv.w, kv.w, s[r]);
                 }
             }
 #pragma unroll
@@ -368,11 +365,11 @@ la_fast_kernel(const __nv_bfloat16* __restrict__ proj, long row_stride, int q_of
                 float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                 for (int j = 0; j < n; ++j) {
                     const float vw = v_s[j * LA_VT + lane] * pw[n - 1 - j];
-                    const float4 ka = *reinterpret_cast<const float4*>(k_s + j * D + dbase + g);
+                    const float4 ka = *reinterpret_cast<const float4*>(k_s + j * KS + dbase + g);
                     acc[0] = fmaf(ka.x, vw, acc[0]); acc[1] = fmaf(ka.y, vw, acc[1]);
                     acc[2] = fmaf(ka.z, vw, acc[2]); acc[3] = fmaf(ka.w, vw, acc[3]);
                     if (two) {
-                        const float4 kb = *reinterpret_cast<const float4*>(k_s + j * D + dbase + g + 4);
+                        const float4 kb = *reinterpret_cast<const float4*>(k_s + j * KS + dbase + g + 4);
                         acc[4] = fmaf(kb.x, vw, acc[4]); acc[5] = fmaf(kb.y, vw, acc[5]);
                         acc[6] = fmaf(kb.z, vw, acc[6]); acc[7] = fmaf(kb.w, vw, acc[7]);
                     }
