@@ -138,6 +138,16 @@ def test_attention_with_a_window_kept_first_tokens_and_sinks(dtype, H, G, hd, wi
         kernels.attention(step, q, out, H, G, hd, scale, window, io, keep_first=keep, sinks=sinks)
         ref = torch.cat([w[p:p + n] for w, p, n in zip(want, past, new)])
         torch.testing.assert_close(out.float().cpu(), ref, **_tol(dtype, (2e-5, 1e-4), (2e-2, 2e-2)))
+        # a gate a head, in columns of wider rows: the kernel that says it applied it did, the others left it alone
+        gates = _r(T, H + 11, seed=31, scale=2.0, dtype=dtype)[:, 3:3 + H]
+        gated = kernels.attention(step, q, out, H, G, hd, scale, window, io, keep_first=keep, sinks=sinks, head_gate=gates,
+                                  head_gate_mult=1.3)
+        if gated:
+            factor = (torch.sigmoid(gates.float().cpu()) * 1.3).repeat_interleave(hd, dim=1)
+            torch.testing.assert_close(out.float().cpu(), ref * factor, **_tol(dtype, (2e-5, 1e-4), (2e-2, 2e-2)))
+        else:
+            torch.testing.assert_close(out.float().cpu(), ref, **_tol(dtype, (2e-5, 1e-4), (2e-2, 2e-2)))
+        assert gated == (dtype == torch.bfloat16 and new == [1, 1] and hd in (64, 128) and (keep > 0 and window is not None or sink))
     if window is not None and window + 64 < 300:
         # the decoded token of the long sequence once more, with every page that lies wholly behind its window and
         # holds no kept token poisoned

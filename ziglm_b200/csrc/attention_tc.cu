@@ -381,14 +381,22 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
 
 // out[t, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), splits in order.
 // sinks (float, one per head, or null): exp(sinks[h]) joins the denominator of head h.
+// head_gate (or null): head h of token t is multiplied by sigmoid(head_gate[t * gate_stride + h]) * gate_mult
+// before it is rounded.
 template <int HD>
 __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                   __nv_bfloat16* __restrict__ out, int n_splits, const float* __restrict__ sinks = nullptr,
-                                  int n_heads = 1) {
+                                  int n_heads = 1, const __nv_bfloat16* __restrict__ head_gate = nullptr,
+                                  long gate_stride = 0, float gate_mult = 1.0f) {
     pdl_launch_dependents();
     pdl_wait();
     const long row = blockIdx.x;                    // t * n_heads + h
     const float sink = sinks != nullptr ? sinks[row % n_heads] * 1.4426950408889634f : -INFINITY;
+    float factor = 1.0f;
+    if (head_gate != nullptr) {
+        const float g = __bfloat162float(head_gate[(row / n_heads) * gate_stride + row % n_heads]);
+        factor = (1.0f / (1.0f + expf(-g))) * gate_mult;
+    }
     float big = sink;
     for (int s = 0; s < n_splits; ++s) big = fmaxf(big, part_ml[(row * n_splits + s) * 2]);
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
@@ -400,7 +408,7 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
             den += part_ml[(row * n_splits + s) * 2 + 1] * wgt;
         }
         if (sinks != nullptr) den += exp2f(sink - big);
-        out[row * HD + d] = __float2bfloat16_rn(acc / den);
+        out[row * HD + d] = __float2bfloat16_rn((acc / den) * factor);
     }
 }
 
@@ -1112,9 +1120,11 @@ using namespace zlm;
 // Decode-style attention: every token is a tile of its own (its query heads grouped by kv head).
 // part_o: float [T * n_heads * n_splits * hd], part_ml: float [T * n_heads * n_splits * 2] (scratch).
 // keep_first: with a window, the first positions of a sequence that stay visible behind it.  sinks: float [n_heads]
-// or null; exp(sinks[h]) joins head h's denominator.
+// or null; exp(sinks[h]) joins head h's denominator.  head_gate: bf16 rows of gate_stride elements with one gate per
+// query head in front, or null; head h of token t leaves multiplied by sigmoid(head_gate[t][h]) * gate_mult.
 ZLM_EXPORT int zlm_attention_decode(const void* q, long q_row_stride, void* out, int T, int n_heads, int n_kv, int hd,
                                     float scale, float softcap, int window, int keep_first, const float* sinks,
+                                    const void* head_gate, long gate_stride, float gate_mult,
                                     const int* positions, const int* seq_of_token,
                                     const int* block_table, int bt_stride, const void* k_pages, const void* v_pages,
                                     long n_pages, int page_size, int n_splits, float* part_o, float* part_ml,
@@ -1139,7 +1149,8 @@ ZLM_EXPORT int zlm_attention_decode(const void* q, long q_row_stride, void* out,
                                    positions, seq_of_token, part_o, part_ml);
         if (e == cudaSuccess)
             e = launch_pdl(attn_merge_kernel<128>, dim3(T * n_heads), dim3(128), 0, stream, (const float*)part_o,
-                           (const float*)part_ml, (__nv_bfloat16*)out, n_splits, sinks, n_heads);
+                           (const float*)part_ml, (__nv_bfloat16*)out, n_splits, sinks, n_heads,
+                           (const __nv_bfloat16*)head_gate, gate_stride, gate_mult);
         if (e != cudaSuccess) return (int)e;
     } else {
         static bool done = false;
@@ -1149,7 +1160,8 @@ ZLM_EXPORT int zlm_attention_decode(const void* q, long q_row_stride, void* out,
                                    positions, seq_of_token, part_o, part_ml);
         if (e == cudaSuccess)
             e = launch_pdl(attn_merge_kernel<64>, dim3(T * n_heads), dim3(64), 0, stream, (const float*)part_o,
-                           (const float*)part_ml, (__nv_bfloat16*)out, n_splits, sinks, n_heads);
+                           (const float*)part_ml, (__nv_bfloat16*)out, n_splits, sinks, n_heads,
+                           (const __nv_bfloat16*)head_gate, gate_stride, gate_mult);
         if (e != cudaSuccess) return (int)e;
     }
     return launch_status();

@@ -118,7 +118,7 @@ _PROTOTYPES = {
     },
     "attention_tc": {
         "zlm_attention_decode": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_int,
-                                 c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int,
+                                 c_void_p, c_void_p, c_long, c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int,
                                  c_void_p, c_void_p, c_void_p],
         "zlm_attention_decode_flat": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p,
                                       c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p,
@@ -873,9 +873,11 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: i
                      window: Optional[int], positions: torch.Tensor, seq_of_token: torch.Tensor,
                      block_table: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_size: int,
                      n_splits: int, part_o: torch.Tensor, part_ml: torch.Tensor, softcap: float = 0.0,
-                     keep_first: int = 0, sinks: Optional[torch.Tensor] = None) -> bool:
+                     keep_first: int = 0, sinks: Optional[torch.Tensor] = None,
+                     head_gate: Optional[torch.Tensor] = None, head_gate_mult: float = 1.0) -> bool:
     """Tensor-core attention for steps of one token per sequence (bf16, head size 64 or 128); ``keep_first`` and
-    ``sinks`` as :func:`attention_general` takes them.
+    ``sinks`` as :func:`attention_general` takes them.  ``head_gate`` ([T, n_heads] of the rows' type, a row stride of
+    its own): head h of token t leaves multiplied by sigmoid(head_gate[t, h]) * ``head_gate_mult``.
 
     Each token's query heads are grouped by key/value head so that the cache is read once per group; the keys
     of a sequence are split over ``n_splits`` blocks whose partial results go through the float32 scratch
@@ -898,9 +900,14 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: i
         _cuda(sinks, "sinks", torch.float32)
         if sinks.numel() != n_heads or not sinks.is_contiguous():
             raise KernelError("attention_decode: one sink per query head is needed")
+    if head_gate is not None:
+        _rows(head_gate, "head_gate")
+        if head_gate.dtype != qkv.dtype or tuple(head_gate.shape) != (T, n_heads):
+            raise KernelError("attention_decode: the gates must be [T, n_heads] of the rows' type")
     status = _fn("attention_tc", "zlm_attention_decode")(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, n_heads, n_kv, head_dim, scale, float(softcap or 0.0),
-        int(window or 0), int(keep_first or 0) if window else 0, _ptr(sinks),
+        int(window or 0), int(keep_first or 0) if window else 0, _ptr(sinks), _ptr(head_gate),
+        _row_stride(head_gate) if head_gate is not None else 0, float(head_gate_mult),
         positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0),
         k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, n_splits, part_o.data_ptr(),
         part_ml.data_ptr(), _stream())
@@ -1107,14 +1114,19 @@ def attention_with_rope(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int
 
 def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
               window: Optional[int], io, softcap: float = 0.0, gate: Optional[torch.Tensor] = None,
-              keep_first: int = 0, sinks: Optional[torch.Tensor] = None) -> bool:
+              keep_first: int = 0, sinks: Optional[torch.Tensor] = None, head_gate: Optional[torch.Tensor] = None,
+              head_gate_mult: float = 1.0) -> bool:
     """Attention of a step's tokens over the cache of the running layer; picks the kernel.  ``softcap`` c > 0:
     the scaled scores become c * tanh(score / c).  ``keep_first``: with a window, the first positions of a sequence
     that stay visible behind it.  ``sinks`` (float32, one per query head): a number in the softmax's denominator that
     belongs to no key.  ``gate`` ([T, n_heads * head_dim] of the step's type): the flat
     decode kernel multiplies its output by sigmoid(gate) before rounding it; the result says whether that was done
     (the caller multiplies when it was not: in a prompt one pass of ``sigmoid_mul`` over coalesced rows costs less
-    than the same work in the prompt kernel's epilogue, where every thread walks a row of its own)."""
+    than the same work in the prompt kernel's epilogue, where every thread walks a row of its own).  ``head_gate``
+    ([T, n_heads], instead of ``gate``): one gate a head, times ``head_gate_mult``; the decode kernel that splits a
+    sequence's keys applies it where it combines the splits, and the result says so likewise."""
+    if gate is not None and head_gate is not None:
+        raise KernelError("attention: a gate an element or a gate a head, not both")
     keep_first = int(keep_first or 0) if window else 0
     # kept first tokens and sinks: the tcgen05 prompt kernel and the decode kernel that splits a sequence's keys
     # know both, the other tensor-core kernels neither
@@ -1127,8 +1139,9 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
             part_ml = step.ws.buf("attn_part_ml", (step.n_tokens * n_heads * n_splits * 2,), torch.float32)
             if attention_decode(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions, step.seq_of_token,
                                 io.block_table, io.k_pages, io.v_pages, io.page_size, n_splits, part_o, part_ml,
-                                softcap=softcap, keep_first=keep_first, sinks=sinks):
-                return False
+                                softcap=softcap, keep_first=keep_first, sinks=sinks, head_gate=head_gate,
+                                head_gate_mult=head_gate_mult):
+                return head_gate is not None
         elif step.max_new >= 16 and attention_prefill_fmha(
                 qkv, out, step.n_seqs, step.max_new, n_heads, n_kv, head_dim, scale, window, step.cu_seqlens,
                 step.past_lens, io.block_table, io.k_pages, io.v_pages, io.page_size, softcap=softcap,

@@ -216,13 +216,16 @@ class CappedAttention(Part):
                                     io.block_table, k_pages, v_pages, io.page_size)
         out = step.ws.buf("attn_out", (T, H * P), self.dtype)
         gate = proj[:, heads_width:] if self.gate == "sigmoid" else None
-        # the flat decode kernel multiplies by the gate's sigmoid as it stores; behind the others a kernel does
+        # the flat decode kernel multiplies by an element gate's sigmoid as it stores, the decode kernel that splits a
+        # sequence's keys by a head's gate where it combines the splits; behind the others a kernel does
+        head_gate = proj[:, heads_width:heads_width + H] if self.gate == "sigmoid_head" else None
         gated = kernels.attention(step, proj, out, H, G, P, self.scale, self.window, io, softcap=self.softcap, gate=gate,
-                                  keep_first=self.keep_first, sinks=self.sinks)
+                                  keep_first=self.keep_first, sinks=self.sinks, head_gate=head_gate,
+                                  head_gate_mult=self.out_scale)
         if self.gate == "sigmoid" and not gated:
             kernels.sigmoid_mul(out, gate, out)
-        elif self.gate == "sigmoid_head":
-            kernels.gate_heads(out, proj[:, heads_width:heads_width + H], out, H, self.out_scale)
+        elif self.gate == "sigmoid_head" and not gated:
+            kernels.gate_heads(out, head_gate, out, H, self.out_scale)
         self.o(out, residual, accumulate=accumulate)
         return None
 
