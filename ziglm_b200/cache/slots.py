@@ -85,11 +85,16 @@ class FreeList:
 class GroupPages:
     """Pages of one group of layers: the pool and, per slot, the pages by position."""
 
-    def __init__(self, n_pages: int, page_size: int, window: Optional[int], keep_first: int = 0):
-        """``keep_first``: with a window, the first positions of a sequence that stay visible behind it."""
+    def __init__(self, n_pages: int, page_size: int, window: Optional[int], keep_first: int = 0,
+                 chunk: Optional[int] = None):
+        """``keep_first``: with a window, the first positions of a sequence that stay visible behind it.  ``chunk``
+        (instead of a window): only the keys of the running chunk of that many positions are ever read again."""
+        if window is not None and chunk is not None:
+            raise ValueError("a group of layers has a window or chunks, not both")
         self.pool = FreeList(n_pages, "page")
         self.page_size = page_size
         self.window = window
+        self.chunk = None if chunk is None else int(chunk)
         self.keep_first = max(0, int(keep_first)) if window is not None else 0
         self.pages_of: Dict[int, List[int]] = {}     # slot -> page per block index (-1: released)
         self.table: Optional[np.ndarray] = None      # the same as rows of an int32 array, once its size is known
@@ -116,9 +121,10 @@ class GroupPages:
     def release_behind_window(self, slot: int, length: int) -> None:
         """Give back pages whose every position lies before the window of the next token, but for the pages that
         hold the first positions the window keeps."""
-        if self.window is None:
+        if self.window is None and self.chunk is None:
             return
-        first_visible = max(0, length - self.window + 1)    # the next token sits at position `length`
+        # the next token sits at position `length`
+        first_visible = max(0, length - self.window + 1) if self.chunk is None else length - length % self.chunk
         pages = self.pages_of.get(slot, [])
         kept_pages = -(-self.keep_first // self.page_size)
         for i in range(kept_pages, min(len(pages), first_visible // self.page_size)):

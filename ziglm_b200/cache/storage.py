@@ -31,7 +31,7 @@ class KVGroup:
         self.need = need
         self.places = places
         self.page_size = page_size
-        self.pages = GroupPages(n_pages, page_size, need.window, need.keep_first)
+        self.pages = GroupPages(n_pages, page_size, need.window, need.keep_first, need.chunk)
         shape = (len(places), n_pages, need.n_kv_heads, page_size, need.head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         # a latent that is key and value at once is kept once

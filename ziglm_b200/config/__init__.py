@@ -3,6 +3,7 @@ from .llama import LlamaConfig, RopeScaling
 from .tumatar import TumatarConfig
 from .tikalix import TikalixConfig
 from .vilazen import VilazenConfig
+from .lipadra import LipadraConfig
 from .registry import (config_from_dict, config_from_folder, register_architecture,
                        registered_architectures, unregister_architecture)
 from .shapes import SHAPES, shape
@@ -10,7 +11,7 @@ from .spec import (FeedForwardSpec, HookSpec, LayerSpec, MixerSpec, ModelSpec, N
                    PositionSpec)
 
 __all__ = [
-    "ConfigError", "LlamaConfig", "TumatarConfig", "TikalixConfig", "VilazenConfig", "SHAPES", "shape", "RopeScaling", "read_config_json",
+    "ConfigError", "LlamaConfig", "TumatarConfig", "TikalixConfig", "VilazenConfig", "LipadraConfig", "SHAPES", "shape", "RopeScaling", "read_config_json",
     "config_from_dict", "config_from_folder", "register_architecture",
     "registered_architectures", "unregister_architecture",
     "FeedForwardSpec", "HookSpec", "LayerSpec", "MixerSpec", "ModelSpec", "NormSpec", "PositionSpec",

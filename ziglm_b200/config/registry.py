@@ -17,6 +17,7 @@ from .llama import LlamaConfig
 from .tumatar import TumatarConfig
 from .tikalix import TikalixConfig
 from .vilazen import VilazenConfig
+from .lipadra import LipadraConfig
 from .spec import ModelSpec
 
 _ARCHITECTURES: Dict[str, Any] = {}
@@ -68,3 +69,4 @@ register_architecture(LlamaConfig.ARCHITECTURE, LlamaConfig)
 register_architecture(TumatarConfig.ARCHITECTURE, TumatarConfig)
 register_architecture(TikalixConfig.ARCHITECTURE, TikalixConfig)
 register_architecture(VilazenConfig.ARCHITECTURE, VilazenConfig)
+register_architecture(LipadraConfig.ARCHITECTURE, LipadraConfig)

@@ -196,6 +196,7 @@ template <typename T>
 __global__ void __launch_bounds__(RNS_WARPS * 32)
 rope_norm_store_kernel(T* __restrict__ qkv, long row_stride, int n_heads, int n_kv, int hd, int rot,
                        const float* __restrict__ inv_freq, float amplitude, int norm_dim, float norm_eps,
+                       int norm_first, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
                        const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                        const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_pages,
                        T* __restrict__ v_pages, int page_size, long page_stride) {
@@ -244,6 +245,16 @@ rope_norm_store_kernel(T* __restrict__ qkv, long row_stride, int n_heads, int n_
         for (int i = lane; i < hd; i += 32) hs[i] = to_float(row[i]);
         __syncwarp();
         float ss = 0.f;
+        if (norm_first && norm_dim > 0) {
+            // the norm stands before the rotation and has a weight that all heads of a kind share
+            for (int i = lane; i < norm_dim; i += 32) ss = fmaf(hs[i], hs[i], ss);
+            ss = warp_sum(ss);
+            const float inv0 = 1.0f / sqrtf(ss / (float)norm_dim + norm_eps);
+            const float* w = head < n_heads ? q_weight : k_weight;
+            for (int i = lane; i < norm_dim; i += 32) hs[i] = (hs[i] * inv0) * (w ? w[i] : 1.0f);
+            __syncwarp();
+            ss = 0.f;
+        }
         float vals[ATT_MAX_HD_ROPE / 32];
 #pragma unroll
         for (int r = 0; r < ATT_MAX_HD_ROPE / 32; ++r) {
@@ -258,7 +269,7 @@ rope_norm_store_kernel(T* __restrict__ qkv, long row_stride, int n_heads, int n_
             vals[r] = v;
         }
         float inv = 1.0f;
-        if (norm_dim > 0) {
+        if (norm_dim > 0 && !norm_first) {
             ss = warp_sum(ss);
             inv = 1.0f / sqrtf(ss / (float)norm_dim + norm_eps);
         }
@@ -283,6 +294,7 @@ rope_norm_store_kernel(T* __restrict__ qkv, long row_stride, int n_heads, int n_
 __global__ void __launch_bounds__(RNS_WARPS * 32)
 rope_norm_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, long row_stride, int n_heads, int n_kv, int hd, int rot,
                            const float* __restrict__ inv_freq, float amplitude, int norm_dim, float norm_eps,
+                           int norm_first, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
                            const int* __restrict__ positions, const int* __restrict__ seq_of_token,
                            const int* __restrict__ block_table, int bt_stride, __nv_bfloat16* __restrict__ k_pages,
                            __nv_bfloat16* __restrict__ v_pages, int page_size, long page_stride, int lph) {
@@ -344,6 +356,31 @@ rope_norm_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, long row_stride, int
                     const float2 y = __bfloat1622float2(hp[k]);
                     b[2 * k] = y.x; b[2 * k + 1] = y.y;
                 }
+            }
+        }
+        if (norm_first && norm_dim > 0) {
+            // the norm stands before the rotation and has a weight that all heads of a kind share
+            if (active) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (i0 + k < norm_dim) ss = fmaf(a[k], a[k], ss);
+                    if (pair && i0 + half + k < norm_dim) ss = fmaf(b[k], b[k], ss);
+                }
+            }
+            for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float inv0 = 1.0f / sqrtf(ss / (float)norm_dim + norm_eps);
+            if (active) {
+                const float* w = head < n_heads ? q_weight : k_weight;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (i0 + k < norm_dim) a[k] = (a[k] * inv0) * (w ? w[i0 + k] : 1.0f);
+                    if (pair && i0 + half + k < norm_dim) b[k] = (b[k] * inv0) * (w ? w[i0 + half + k] : 1.0f);
+                }
+            }
+            ss = 0.f;
+        }
+        if (active) {
+            if (pair) {
 #pragma unroll
                 for (int k = 0; k < 8; ++k) {
                     const float c = cos_s[i0 + k], sn = sin_s[i0 + k];
@@ -358,7 +395,7 @@ rope_norm_store_vec_kernel(__nv_bfloat16* __restrict__ qkv, long row_stride, int
                 if (i0 + k < norm_dim) ss = fmaf(a[k], a[k], ss);
         }
         float inv = 1.0f;
-        if (norm_dim > 0) {
+        if (norm_dim > 0 && !norm_first) {
             for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             inv = 1.0f / sqrtf(ss / (float)norm_dim + norm_eps);
         }
@@ -453,7 +490,7 @@ attention_general_kernel(const T* __restrict__ q, long q_row_stride, T* __restri
     const int pos = positions[t];
     const int b = seq_of_token[t];
     const int kvh = h0 / (n_heads / n_kv);
-    const int start = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int start = first_visible_key(pos, window);
     // the keys a token sees, counted through: the first tokens a window keeps (those before the window), then the window
     const int kept = min(keep_first, start);
     const int n_keys = kept + pos - start + 1;
@@ -618,7 +655,7 @@ attention_fold_kernel(T* __restrict__ out, int n_heads, int hd, int window, int 
                       const float* __restrict__ part_ml, const float* __restrict__ part_o, int max_parts) {
     const int t = blockIdx.x, h = blockIdx.y;
     const int pos = positions[t];
-    const int start = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int start = first_visible_key(pos, window);
     const int n_parts = (min(keep_first, start) + pos - start + 1 + ATT_PART - 1) / ATT_PART;
     const float* ml = part_ml + ((long)t * n_heads + h) * max_parts * 2;
     const float* po = part_o + ((long)t * n_heads + h) * max_parts * hd;
@@ -996,9 +1033,12 @@ ZLM_EXPORT int zlm_rope_store(void* qkv, int dtype, long row_stride, int T, int 
 // Like zlm_rope_store for rows [q heads | k heads | v heads | anything else] (row_stride elements a row), with the
 // cosines and sines multiplied by `amplitude` and, when norm_dim > 0, every rotated q and k head divided by the
 // root of (the mean of the squares of its first norm_dim dimensions + norm_eps) before it is written back and
-// stored.  inv_freq == nullptr: no rotation.  k_pages == nullptr: nothing is stored.
+// stored.  inv_freq == nullptr: no rotation.  k_pages == nullptr: nothing is stored.  norm_first != 0: the norm stands
+// BEFORE the rotation instead, and q_weight / k_weight (float [hd], shared by all query / key heads; nullptr: none)
+// multiply the normed heads.
 ZLM_EXPORT int zlm_rope_norm_store(void* qkv, int dtype, long row_stride, int T, int n_heads, int n_kv, int hd, int rot,
                                    const float* inv_freq, float amplitude, int norm_dim, float norm_eps,
+                                   int norm_first, const float* q_weight, const float* k_weight,
                                    const int* positions, const int* seq_of_token, const int* block_table, int bt_stride,
                                    void* k_pages, void* v_pages, int page_size, long page_stride, cudaStream_t stream) {
     if (T <= 0) return 0;
@@ -1014,8 +1054,9 @@ ZLM_EXPORT int zlm_rope_norm_store(void* qkv, int dtype, long row_stride, int T,
     cudaError_t e;
     if (dtype == ZLM_F32)
         e = launch_pdl(rope_norm_store_kernel<float>, grid, dim3(RNS_WARPS * 32), 0, stream, (float*)qkv, row_stride,
-                       n_heads, n_kv, hd, rot, inv_freq, amplitude, norm_dim, norm_eps, positions, seq_of_token,
-                       block_table, bt_stride, (float*)k_pages, (float*)v_pages, page_size, page_stride);
+                       n_heads, n_kv, hd, rot, inv_freq, amplitude, norm_dim, norm_eps, norm_first, q_weight, k_weight,
+                       positions, seq_of_token, block_table, bt_stride, (float*)k_pages, (float*)v_pages, page_size,
+                       page_stride);
     else if (dtype == ZLM_BF16 && hd % 8 == 0 && (inv_freq == nullptr || rot % 16 == 0) && row_stride % 8 == 0 &&
              page_stride % 8 == 0 && (uintptr_t)qkv % 16 == 0 && (uintptr_t)k_pages % 16 == 0 &&
              (uintptr_t)v_pages % 16 == 0 && hd / 8 <= 32) {
@@ -1029,13 +1070,14 @@ ZLM_EXPORT int zlm_rope_norm_store(void* qkv, int dtype, long row_stride, int T,
         if (vparts > most) vparts = most;
         if (vparts < 1) vparts = 1;
         e = launch_pdl(rope_norm_store_vec_kernel, dim3(T, vparts), dim3(RNS_WARPS * 32), 0, stream, (__nv_bfloat16*)qkv,
-                       row_stride, n_heads, n_kv, hd, rot, inv_freq, amplitude, norm_dim, norm_eps, positions, seq_of_token,
-                       block_table, bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size, page_stride, lph);
+                       row_stride, n_heads, n_kv, hd, rot, inv_freq, amplitude, norm_dim, norm_eps, norm_first, q_weight,
+                       k_weight, positions, seq_of_token, block_table, bt_stride, (__nv_bfloat16*)k_pages,
+                       (__nv_bfloat16*)v_pages, page_size, page_stride, lph);
     } else if (dtype == ZLM_BF16)
         e = launch_pdl(rope_norm_store_kernel<__nv_bfloat16>, grid, dim3(RNS_WARPS * 32), 0, stream, (__nv_bfloat16*)qkv,
-                       row_stride, n_heads, n_kv, hd, rot, inv_freq, amplitude, norm_dim, norm_eps, positions,
-                       seq_of_token, block_table, bt_stride, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, page_size,
-                       page_stride);
+                       row_stride, n_heads, n_kv, hd, rot, inv_freq, amplitude, norm_dim, norm_eps, norm_first, q_weight,
+                       k_weight, positions, seq_of_token, block_table, bt_stride, (__nv_bfloat16*)k_pages,
+                       (__nv_bfloat16*)v_pages, page_size, page_stride);
     else
         return ZLM_ERR_UNSUPPORTED;
     return e == cudaSuccess ? launch_status() : (int)e;

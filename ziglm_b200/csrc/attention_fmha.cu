@@ -207,7 +207,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         rows_t[t] = max(0, min(FM_BQ, n_new - q0 - t * FM_BQ));
         const int pf = past + q0 + t * FM_BQ;
         pos_last_t[t] = pf + max(rows_t[t], 1) - 1;
-        const int sf = (a.window > 0 && pf - a.window + 1 > 0) ? pf - a.window + 1 : 0;
+        const int sf = first_visible_key(pf, a.window);
         plo_t[t] = sf / FM_PAGE;
         phi_t[t] = pos_last_t[t] / FM_PAGE + 1;
     }
@@ -394,7 +394,7 @@ fmha_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const bool real = r < rows_t[t];
         // rows beyond the sequence's tokens compute like its last row and are never stored
         const int pos = real ? past + q0 + t * FM_BQ + r : pos_last_t[t];
-        const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+        const int start = first_visible_key(pos, a.window);
         const float scale = a.scale_log2;
         const float neg_big = -3.0e38f;                               // stands for a masked score before scaling
         float m = -INFINITY, l = 0.f;

@@ -261,7 +261,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
     const int n_splits = gridDim.x, split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
     const int group = a.n_heads / a.n_kv;
     const int pos = positions[t];
-    const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+    const int start = first_visible_key(pos, a.window);
     const int* bt = a.block_table + (long)seq_of_token[t] * a.bt_stride;
     const int first_page = start / PAGE, end_page = pos / PAGE + 1;
     // the list of pages: those of the kept first positions that lie before the window's first page, then the window's
@@ -549,7 +549,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
     // the kernel before this one: they may be read before the wait below.
     for (int t = threadIdx.x; t < T; t += blockDim.x) {
         const int pos = positions[t];
-        const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+        const int start = first_visible_key(pos, a.window);
         pre[t + 1] = pos / PAGE + 1 - start / PAGE;
     }
     if (threadIdx.x == 0) pre[0] = 0;
@@ -607,7 +607,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
                 continue;
             }
             const int pos = positions[t];
-            const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+            const int start = first_visible_key(pos, a.window);
             const int* bt = a.block_table + (long)seq_of_token[t] * a.bt_stride + start / PAGE + j;
             const int i_new = p_t - 1 - j;               // index within this run of the page of position pos
             for (int i0 = 0; i0 < seg && alive; i0 += 32) {
@@ -667,7 +667,7 @@ attn_decode_flat_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid
         vi += p_t + IC;
         if (seg <= 0) continue;
         const int pos = positions[t];
-        const int start = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+        const int start = first_visible_key(pos, a.window);
         const int first_page = start / PAGE;
         if (half > 0 && t != t_angles) {
             // cosines and sines of this token's position (float32 angles, as the separate kernel forms them)
@@ -934,7 +934,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     const int* bt = a.block_table + (long)b * a.bt_stride;
     const int rows_here = min(64, n_new - q0);
     const int pos_first = past + q0, pos_last = past + q0 + rows_here - 1;
-    const int start_first = (a.window > 0 && pos_first - a.window + 1 > 0) ? pos_first - a.window + 1 : 0;
+    const int start_first = first_visible_key(pos_first, a.window);
     const int page_lo = start_first / PAGE, page_hi = pos_last / PAGE + 1;
 
     if (threadIdx.x == 0) {
@@ -965,12 +965,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
     load_q_frags<HD>(qf, has_lo ? qbase + (long)(tok_begin + r_lo) * a.q_row_stride : nullptr,
                      has_hi ? qbase + (long)(tok_begin + r_hi) * a.q_row_stride : nullptr, tid4);
     const int lim_lo = has_lo ? past + r_lo : -1, lim_hi = has_hi ? past + r_hi : -1;
-    const int st_lo = (a.window > 0 && lim_lo - a.window + 1 > 0) ? lim_lo - a.window + 1 : 0;
-    const int st_hi = (a.window > 0 && lim_hi - a.window + 1 > 0) ? lim_hi - a.window + 1 : 0;
+    const int st_lo = first_visible_key(lim_lo, a.window);
+    const int st_hi = first_visible_key(lim_hi, a.window);
     // the warp's rows span positions [w_first, w_last]: pages wholly outside need no work
     const int w_first = past + q0 + warp * 16, w_last = min(pos_last, w_first + 15);
-    const int w_start = (a.window > 0 && w_first - a.window + 1 > 0) ? w_first - a.window + 1 : 0;
-    const int w_last_start = (a.window > 0 && w_last - a.window + 1 > 0) ? w_last - a.window + 1 : 0;
+    const int w_start = first_visible_key(w_first, a.window);
+    const int w_last_start = first_visible_key(w_last, a.window);
     const bool w_rows_all = w_first + 15 <= pos_last;        // all 16 rows of the warp are real tokens
 
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};

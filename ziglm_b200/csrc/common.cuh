@@ -81,6 +81,15 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// The first key a query at position `pos` of its sequence sees.  window > 0: a sliding window of that many
+// positions; window < 0: chunks of -window positions counted from the start of the sequence, a query seeing the keys
+// of its own chunk only; 0: every earlier key.  The result never decreases as pos grows.
+__host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
+    if (window > 0) return pos - window + 1 > 0 ? pos - window + 1 : 0;
+    if (window < 0) return pos - pos % (-window);
+    return 0;
+}
+
 // Programmatic dependent launch: a kernel launched with launch_pdl may become resident while the
 // kernels before it in the stream are still running.  It must call pdl_wait() before it reads what
 // a kernel of the same step wrote or writes what one may read; pdl_launch_dependents() lets the

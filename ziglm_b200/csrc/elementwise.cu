@@ -307,6 +307,86 @@ __global__ void norm_add_scaled_kernel(const float* __restrict__ branch, const T
     }
 }
 
+// The norm of a sum, in place: with s = alpha * x[r] + branch[r],
+//   x[r] = s / sqrt(mean(s^2) + eps) * (w + off);   h[r] = x[r]      (h may be null)
+// The residual stream of an arrangement whose norms stand behind the sums: the stream itself is normed.
+template <typename TW, typename TO, bool VEC>
+__global__ void sum_norm_kernel(const float* __restrict__ branch, const TW* __restrict__ w, float off, float eps,
+                                float alpha, float* __restrict__ x, TO* __restrict__ h, int d) {
+    __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* br = branch + (long)blockIdx.x * d;
+    float* xr = x + (long)blockIdx.x * d;
+    float ss = 0.f;
+    if constexpr (VEC) {
+        const int n4 = d >> 2;
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 b4 = reinterpret_cast<const float4*>(br)[i];
+            const float4 v = reinterpret_cast<const float4*>(xr)[i];
+            const float s0 = fmaf(alpha, v.x, b4.x), s1 = fmaf(alpha, v.y, b4.y), s2 = fmaf(alpha, v.z, b4.z),
+                        s3 = fmaf(alpha, v.w, b4.w);
+            ss = fmaf(s0, s0, ss); ss = fmaf(s1, s1, ss); ss = fmaf(s2, s2, ss); ss = fmaf(s3, s3, ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            const float4 b4 = reinterpret_cast<const float4*>(br)[i];
+            float4 v = reinterpret_cast<const float4*>(xr)[i];
+            float ww[4];
+            load4<TW>(w + 4 * i, ww);
+            v.x = (fmaf(alpha, v.x, b4.x) * inv) * (ww[0] + off); v.y = (fmaf(alpha, v.y, b4.y) * inv) * (ww[1] + off);
+            v.z = (fmaf(alpha, v.z, b4.z) * inv) * (ww[2] + off); v.w = (fmaf(alpha, v.w, b4.w) * inv) * (ww[3] + off);
+            reinterpret_cast<float4*>(xr)[i] = v;
+            if (h != nullptr) store4<TO>(h + (long)blockIdx.x * d + 4 * i, v.x, v.y, v.z, v.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float s = fmaf(alpha, xr[i], br[i]);
+            ss = fmaf(s, s, ss);
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+        for (int i = threadIdx.x; i < d; i += blockDim.x) {
+            const float v = (fmaf(alpha, xr[i], br[i]) * inv) * (to_float(w[i]) + off);
+            xr[i] = v;
+            if (h != nullptr) h[(long)blockIdx.x * d + i] = from_float<TO>(v);
+        }
+    }
+}
+
+// A norm of every head by itself, with a gate: row r of x (float) holds n_heads heads of hd elements;
+//   out[r, h, i] = x[r, h, i] / sqrt(mean_i x[r, h, :]^2 + eps) * w[h * hd + i] * act(g[r, h * hd + i]) * mult
+// w null: no weight.  gate_kind 0: no gate, 1: sigmoid(g), 2: silu(g) = g sigmoid(g).  One warp a head.
+constexpr int HNG_WARPS = 4;
+template <typename T>
+__global__ void __launch_bounds__(HNG_WARPS * 32)
+head_norm_gate_kernel(const float* __restrict__ x, long x_stride, const float* __restrict__ w, const T* __restrict__ g,
+                      long g_stride, T* __restrict__ out, long out_stride, long n_pairs, int n_heads, int hd, float eps,
+                      int gate_kind, float mult) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long pair = (long)blockIdx.x * HNG_WARPS + (threadIdx.x >> 5);
+    if (pair >= n_pairs) return;
+    const long r = pair / n_heads;
+    const int h = (int)(pair % n_heads);
+    const float* xr = x + r * x_stride + (long)h * hd;
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)hd + eps);
+    for (int i = lane; i < hd; i += 32) {
+        float y = xr[i] * inv;
+        if (w != nullptr) y *= w[(long)h * hd + i];
+        if (gate_kind != 0) {
+            const float gv = to_float(g[r * g_stride + (long)h * hd + i]);
+            const float sg = 1.0f / (1.0f + expf(-gv));
+            y *= gate_kind == 2 ? gv * sg : sg;
+        }
+        out[r * out_stride + (long)h * hd + i] = from_float<T>(y * mult);
+    }
+}
+
 // out[i] = act(x[i]); kind 0: the squared relu, max(x, 0)^2; kind 1: the exact gelu, x (1 + erf(x / sqrt 2)) / 2
 template <typename T>
 __global__ void unary_act_kernel(const T* __restrict__ x, T* __restrict__ out, long n, int kind) {
@@ -762,6 +842,30 @@ ZLM_EXPORT int zlm_norm_add_scaled(const float* branch, const void* w, int w_dty
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 
+// x rows (float, contiguous) = RMS norm (gain w + off) of alpha * x + branch rows (float, contiguous); h (may be null):
+// the new rows of x in h_dtype.
+ZLM_EXPORT int zlm_sum_norm(const float* branch, const void* w, int w_dtype, float off, float eps, float alpha, float* x,
+                            void* h, int h_dtype, int n_rows, int d, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (d <= 0) return ZLM_ERR_BAD_ARG;
+    const bool vec = d % 4 == 0 && (uintptr_t)branch % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 &&
+                     (uintptr_t)h % 16 == 0;
+    const int threads = vec ? (d >= 2048 ? 256 : (d >= 512 ? 128 : 64)) : norm_threads(d);
+    cudaError_t e;
+#define ZLM_SN(TW, TO)                                                                                               \
+    e = vec ? launch_pdl(sum_norm_kernel<TW, TO, true>, dim3(n_rows), dim3(threads), 0, stream, branch, (const TW*)w,  \
+                         off, eps, alpha, x, (TO*)h, d)                                                              \
+            : launch_pdl(sum_norm_kernel<TW, TO, false>, dim3(n_rows), dim3(threads), 0, stream, branch, (const TW*)w, \
+                         off, eps, alpha, x, (TO*)h, d)
+    if (w_dtype == ZLM_F32 && (h == nullptr || h_dtype == ZLM_F32)) ZLM_SN(float, float);
+    else if (w_dtype == ZLM_F32 && h_dtype == ZLM_BF16) ZLM_SN(float, __nv_bfloat16);
+    else if (w_dtype == ZLM_BF16 && (h == nullptr || h_dtype == ZLM_F32)) ZLM_SN(__nv_bfloat16, float);
+    else if (w_dtype == ZLM_BF16 && h_dtype == ZLM_BF16) ZLM_SN(__nv_bfloat16, __nv_bfloat16);
+    else return ZLM_ERR_UNSUPPORTED;
+#undef ZLM_SN
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
 // kind 0: the squared relu, 1: the exact gelu.  out may be x.
 ZLM_EXPORT int zlm_unary_act(const void* x, void* out, int dtype, long n, int kind, cudaStream_t stream) {
     if (n <= 0) return 0;
@@ -864,6 +968,28 @@ ZLM_EXPORT int zlm_norm_gate(const float* x, long x_stride, const float* w, cons
     else if (dtype == ZLM_BF16)
         e = launch_pdl(norm_gate_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, w,
                        (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride, d, eps, mult);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+// x: float rows of n_heads * hd elements; every head is divided by its own root mean square; w (float, n_heads * hd,
+// or null), g (rows of the output's type, or null with gate_kind 0), gate_kind 1 sigmoid, 2 silu; out in dtype.
+ZLM_EXPORT int zlm_head_norm_gate(const float* x, long x_stride, const float* w, const void* g, long g_stride, void* out,
+                                  long out_stride, int dtype, int n_rows, int n_heads, int hd, float eps, int gate_kind,
+                                  float mult, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (n_heads <= 0 || hd <= 0 || gate_kind < 0 || gate_kind > 2 || (gate_kind != 0 && g == nullptr)) return ZLM_ERR_BAD_ARG;
+    const long n_pairs = (long)n_rows * n_heads;
+    const unsigned blocks = (unsigned)((n_pairs + HNG_WARPS - 1) / HNG_WARPS);
+    cudaError_t e;
+    if (dtype == ZLM_F32)
+        e = launch_pdl(head_norm_gate_kernel<float>, dim3(blocks), dim3(HNG_WARPS * 32), 0, stream, x, x_stride, w,
+                       (const float*)g, g_stride, (float*)out, out_stride, n_pairs, n_heads, hd, eps, gate_kind, mult);
+    else if (dtype == ZLM_BF16)
+        e = launch_pdl(head_norm_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(HNG_WARPS * 32), 0, stream, x, x_stride, w,
+                       (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, out_stride, n_pairs, n_heads, hd, eps,
+                       gate_kind, mult);
     else
         return ZLM_ERR_UNSUPPORTED;
     return e == cudaSuccess ? launch_status() : (int)e;

@@ -479,6 +479,41 @@ la_decode_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_o
     }
 }
 
+// What stands between the projection and the recurrence when q and k are turned by position: row t of out (float,
+// contiguous, [q heads | k heads | v heads]) takes head h's q and k from proj's row with the first `rot` dimensions
+// of the head turned by the token's position (dimension i together with i + rot/2, angle pos * inv_freq[i]), k
+// also times k_scale, and v as it is.  Everything is float from the read on, so what enters the recurrence never
+// passes through a 16-bit type again.
+template <typename T>
+__global__ void la_prep_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_off, int v_off, int H, int D,
+                               int V, int rot, const float* __restrict__ inv_freq, float k_scale,
+                               const int* __restrict__ positions, float* __restrict__ out, long total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int width = 2 * H * D + H * V;
+    const long t = idx / width;
+    const int col = (int)(idx % width);
+    const T* row = proj + t * row_stride;
+    if (col >= 2 * H * D) {
+        out[idx] = to_float(row[v_off + col - 2 * H * D]);
+        return;
+    }
+    const bool is_k = col >= H * D;
+    const int e = is_k ? col - H * D : col;
+    const int i = e % D;
+    const T* head = row + (is_k ? k_off : q_off) + (e - i);
+    float v = to_float(head[i]);
+    const int half = rot / 2;
+    if (inv_freq != nullptr && i < rot) {
+        float sn, cs;
+        sincosf((float)positions[t] * inv_freq[i < half ? i : i - half], &sn, &cs);
+        v = i < half ? v * cs - to_float(head[i + half]) * sn : v * cs + to_float(head[i - half]) * sn;
+    }
+    out[idx] = is_k ? v * k_scale : v;
+}
+
 }  // namespace zlm
 
 using namespace zlm;
@@ -572,4 +607,25 @@ ZLM_EXPORT int zlm_decayed_linear_attention(const void* proj, int dtype, long ro
         return la_launch((const __nv_bfloat16*)proj, row_stride, q_off, k_off, v_off, H, D, V, act, pows, state, slots,
                          cu_seqlens, n_seqs, n_segments, single_token != 0, seg_state, out, out_stride, stream);
     return ZLM_ERR_UNSUPPORTED;
+}
+
+// proj: rows of `dtype` with head h's q, k, v at q_off + h*D, k_off + h*D, v_off + h*V; out: float [T, 2*H*D + H*V]
+// contiguous.  rot (even, at most D) with inv_freq (float [rot/2]; null: no rotation).
+ZLM_EXPORT int zlm_linear_attention_prep(const void* proj, int dtype, long row_stride, int q_off, int k_off, int v_off,
+                                         int H, int D, int V, int rot, const float* inv_freq, float k_scale,
+                                         const int* positions, float* out, int T, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || D <= 0 || V <= 0 || rot < 0 || rot > D || (rot & 1)) return ZLM_ERR_BAD_ARG;
+    const long total = (long)T * (2L * H * D + (long)H * V);
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaError_t e;
+    if (dtype == ZLM_F32)
+        e = launch_pdl(la_prep_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)proj, row_stride, q_off,
+                       k_off, v_off, H, D, V, rot, inv_freq, k_scale, positions, out, total);
+    else if (dtype == ZLM_BF16)
+        e = launch_pdl(la_prep_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)proj,
+                       row_stride, q_off, k_off, v_off, H, D, V, rot, inv_freq, k_scale, positions, out, total);
+    else
+        return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
 }

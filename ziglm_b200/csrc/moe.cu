@@ -9,7 +9,9 @@
 //   experts form n_groups equal groups of neighbours; a group's score is the sum of its group_best largest
 //   choice scores; only experts of the keep_groups best groups can be chosen (the others count as -inf);
 //   the `top` experts with the largest choice scores are chosen (ties: the lower index), and their weights are
-//   score_e (without the correction), divided by their sum if `renormalize`.
+//   score_e (without the correction), divided by their sum if `renormalize`, times `weight_scale`.
+//   The last experts may be identity experts (n_real < E at the grouping and the products): they have no weights,
+//   their output is the token's row itself, and the sum over a token's pairs takes it from there.
 //
 // Pair p = token * top + k.  The pairs are grouped by expert into `sorted` (offsets per expert in `offs`), and
 // the rows of every expert are cut into tiles of GM rows (`tile_expert`, `tile_row`; `n_tiles[0]` tiles in all).
@@ -42,9 +44,10 @@ constexpr int RT_WARPS = 8;
 
 template <typename TH>
 __global__ void __launch_bounds__(RT_WARPS * 32)
-route_kernel(const float* __restrict__ z, const TH* __restrict__ h, long h_stride, const TH* __restrict__ w, int d,
-             const float* __restrict__ correction, int E, int top, int n_groups, int keep_groups, int group_best,
-             int softmax_scores, int renormalize, int* __restrict__ ids, float* __restrict__ weights) {
+route_kernel(const float* __restrict__ z, long z_stride, const TH* __restrict__ h, long h_stride, const TH* __restrict__ w,
+             int d, const float* __restrict__ correction, int E, int top, int n_groups, int keep_groups, int group_best,
+             int softmax_scores, int renormalize, float weight_scale, int n_extra, float* __restrict__ extra_out,
+             int* __restrict__ ids, float* __restrict__ weights) {
     extern __shared__ float sm[];
     float* score = sm;                 // [E]
     float* choice = sm + E;            // [E]
@@ -55,13 +58,14 @@ route_kernel(const float* __restrict__ z, const TH* __restrict__ h, long h_strid
     pdl_wait();
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (z != nullptr) {
-        for (int e = threadIdx.x; e < E; e += blockDim.x) logit[e] = z[(long)t * E + e];
+        for (int e = threadIdx.x; e < E; e += blockDim.x) logit[e] = z[(long)t * z_stride + e];
     } else {
         for (int i = threadIdx.x; i < d; i += blockDim.x) row[i] = to_float(h[(long)t * h_stride + i]);
         __syncthreads();
         constexpr int V = 16 / (int)sizeof(TH);
         const bool wide = d % V == 0 && (uintptr_t)w % 16 == 0;
-        for (int e = warp; e < E; e += RT_WARPS) {
+        // the rows behind the experts' (n_extra of them) are further products of the same row: their sums go to extra_out
+        for (int e = warp; e < E + n_extra; e += RT_WARPS) {
             const TH* we = w + (long)e * d;
             float acc = 0.f;
             if (wide) {
@@ -75,7 +79,10 @@ route_kernel(const float* __restrict__ z, const TH* __restrict__ h, long h_strid
                 for (int i = lane; i < d; i += 32) acc = fmaf(row[i], to_float(we[i]), acc);
             }
             acc = warp_sum(acc);
-            if (lane == 0) logit[e] = acc;
+            if (lane == 0) {
+                if (e < E) logit[e] = acc;
+                else extra_out[(long)t * n_extra + (e - E)] = acc;
+            }
         }
     }
     __syncthreads();
@@ -164,13 +171,15 @@ route_kernel(const float* __restrict__ z, const TH* __restrict__ h, long h_strid
     }
     if (renormalize && lane == 0)
         for (int k = 0; k < top; ++k) weights[(long)t * top + k] /= wsum;
+    if (weight_scale != 1.0f && lane == 0)
+        for (int k = 0; k < top; ++k) weights[(long)t * top + k] *= weight_scale;
 }
 
 // ------------------------------------------------------------------ grouping
 // one block.  counts -> offsets -> sorted pairs and tiles.
-__global__ void group_kernel(const int* __restrict__ ids, int P, int E, int* __restrict__ offs, int* __restrict__ sorted,
-                             int* __restrict__ place, int* __restrict__ tile_expert, int* __restrict__ tile_row,
-                             int* __restrict__ n_tiles) {
+__global__ void group_kernel(const int* __restrict__ ids, int P, int E, int n_real, int* __restrict__ offs,
+                             int* __restrict__ sorted, int* __restrict__ place, int* __restrict__ tile_expert,
+                             int* __restrict__ tile_row, int* __restrict__ n_tiles) {
     extern __shared__ int smi[];
     int* count = smi;             // [E]
     int* start = smi + E;         // [E + 1]
@@ -185,7 +194,8 @@ __global__ void group_kernel(const int* __restrict__ ids, int P, int E, int* __r
         for (int e = 0; e < E; ++e) {
             start[e] = at;
             offs[e] = at;
-            for (int r = 0; r < count[e]; r += GM) { tile_expert[tiles] = e; tile_row[tiles] = at + r; ++tiles; }
+            // an identity expert (e >= n_real) has no product: its pairs are grouped like the others and make no tile
+            for (int r = 0; e < n_real && r < count[e]; r += GM) { tile_expert[tiles] = e; tile_row[tiles] = at + r; ++tiles; }
             at += count[e];
         }
         start[E] = at;
@@ -405,8 +415,14 @@ __global__ void gather_kernel(const T* __restrict__ x, long x_stride, const int*
     for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
 }
 
-// out[t, :] (+)= sum_k weights[t, k] * y[row(t * top + k), :], row(p) = p, or place[p] when y is in grouped order
+// out[t, :] (+)= sum_k weights[t, k] * y[row(t * top + k), :], row(p) = p, or place[p] when y is in grouped order.
+// ids != null: a pair whose expert is an identity expert (ids[p] >= n_real) adds weights[p] * h[t, :] instead (its row
+// of y was never written).  shared != null: float [T, d], the output of an expert that runs for every token, added
+// times sigmoid(gate[t * gate_stride]) (gate == null: as it is).
+template <typename TH>
 __global__ void combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, const int* __restrict__ place,
+                               const int* __restrict__ ids, int n_real, const TH* __restrict__ h, long h_stride,
+                               const float* __restrict__ shared, const float* __restrict__ gate, long gate_stride,
                                float* __restrict__ out, long total, int d, int top, int accumulate) {
     pdl_launch_dependents();
     pdl_wait();
@@ -417,7 +433,12 @@ __global__ void combine_kernel(const float* __restrict__ y, const float* __restr
     float acc = 0.f;
     for (int k = 0; k < top; ++k) {
         const long p = t * top + k;
-        acc = fmaf(weights[p], y[(place ? (long)place[p] : p) * d + i], acc);
+        if (ids != nullptr && ids[p] >= n_real) acc = fmaf(weights[p], to_float(h[t * h_stride + i]), acc);
+        else acc = fmaf(weights[p], y[(place ? (long)place[p] : p) * d + i], acc);
+    }
+    if (shared != nullptr) {
+        const float g = gate ? 1.0f / (1.0f + expf(-gate[t * gate_stride])) : 1.0f;
+        acc = fmaf(g, shared[idx], acc);
     }
     out[idx] = accumulate ? out[idx] + acc : acc;
 }
@@ -427,26 +448,29 @@ __global__ void combine_kernel(const float* __restrict__ y, const float* __restr
 using namespace zlm;
 
 // z: float [T, E] router logits, or null: then h [T, d] (rows with a stride) and w [E, d] of one storage type are
-// given and the logits are taken here.
-ZLM_EXPORT int zlm_moe_route(const float* z, const void* h, int h_dtype, long h_stride, const void* w, int d,
+// given and the logits are taken here; w then has n_extra more rows behind the experts', whose products with the
+// token's row go to extra_out [T, n_extra] (float).  z_stride: elements between two rows of z (E, or more when the
+// product had further columns).  The chosen scores are multiplied by weight_scale.
+ZLM_EXPORT int zlm_moe_route(const float* z, long z_stride, const void* h, int h_dtype, long h_stride, const void* w, int d,
                              const float* correction, int T, int E, int top, int n_groups, int keep_groups,
-                             int group_best, int softmax_scores, int renormalize, int* ids, float* weights,
-                             cudaStream_t stream) {
+                             int group_best, int softmax_scores, int renormalize, float weight_scale, int n_extra,
+                             float* extra_out, int* ids, float* weights, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || n_groups <= 0 || E % n_groups || keep_groups <= 0 || keep_groups > n_groups ||
-        group_best <= 0 || top > keep_groups * (E / n_groups) || (!z && (!h || !w || d <= 0)))
+        group_best <= 0 || top > keep_groups * (E / n_groups) || (!z && (!h || !w || d <= 0)) || n_extra < 0 ||
+        (z && z_stride < E) || (!z && n_extra > 0 && !extra_out))
         return ZLM_ERR_BAD_ARG;
     const size_t smem = (3 * (size_t)E + n_groups + (z ? 0 : d)) * sizeof(float);
     if (smem > 48 * 1024) return ZLM_ERR_UNSUPPORTED;
     cudaError_t e;
     if (z || h_dtype == ZLM_F32)
-        e = launch_pdl(route_kernel<float>, dim3(T), dim3(RT_WARPS * 32), smem, stream, z, (const float*)h, h_stride,
-                       (const float*)w, d, correction, E, top, n_groups, keep_groups, group_best, softmax_scores,
-                       renormalize, ids, weights);
+        e = launch_pdl(route_kernel<float>, dim3(T), dim3(RT_WARPS * 32), smem, stream, z, z_stride, (const float*)h,
+                       h_stride, (const float*)w, d, correction, E, top, n_groups, keep_groups, group_best, softmax_scores,
+                       renormalize, weight_scale, n_extra, extra_out, ids, weights);
     else if (h_dtype == ZLM_BF16)
-        e = launch_pdl(route_kernel<__nv_bfloat16>, dim3(T), dim3(RT_WARPS * 32), smem, stream, z, (const __nv_bfloat16*)h,
-                       h_stride, (const __nv_bfloat16*)w, d, correction, E, top, n_groups, keep_groups, group_best,
-                       softmax_scores, renormalize, ids, weights);
+        e = launch_pdl(route_kernel<__nv_bfloat16>, dim3(T), dim3(RT_WARPS * 32), smem, stream, z, z_stride,
+                       (const __nv_bfloat16*)h, h_stride, (const __nv_bfloat16*)w, d, correction, E, top, n_groups,
+                       keep_groups, group_best, softmax_scores, renormalize, weight_scale, n_extra, extra_out, ids, weights);
     else
         return ZLM_ERR_UNSUPPORTED;
     return e == cudaSuccess ? launch_status() : (int)e;
@@ -455,14 +479,15 @@ ZLM_EXPORT int zlm_moe_route(const float* z, const void* h, int h_dtype, long h_
 // The most tiles P pairs over E experts can make.
 ZLM_EXPORT long zlm_moe_max_tiles_scratch(int P, int E) { return (long)(P + GM - 1) / GM + E; }
 
-// place[p]: where pair p stands in ``sorted`` (the inverse of it).
-ZLM_EXPORT int zlm_moe_group(const int* ids, int P, int E, int* offs, int* sorted, int* place, int* tile_expert,
+// place[p]: where pair p stands in ``sorted`` (the inverse of it).  The experts from n_real on are identity experts:
+// their pairs are grouped and counted in offs, and get no tiles.
+ZLM_EXPORT int zlm_moe_group(const int* ids, int P, int E, int n_real, int* offs, int* sorted, int* place, int* tile_expert,
                              int* tile_row, int* n_tiles, cudaStream_t stream) {
     if (P <= 0) return 0;
-    if (E <= 0) return ZLM_ERR_BAD_ARG;
+    if (E <= 0 || n_real < 0 || n_real > E) return ZLM_ERR_BAD_ARG;
     const size_t smem = (2 * (size_t)E + 1 + (P <= 1024 ? P : 0)) * sizeof(int);
     if (smem > 48 * 1024) return ZLM_ERR_UNSUPPORTED;
-    cudaError_t e = launch_pdl(group_kernel, dim3(1), dim3(1024), smem, stream, ids, P, E, offs, sorted, place,
+    cudaError_t e = launch_pdl(group_kernel, dim3(1), dim3(1024), smem, stream, ids, P, E, n_real, offs, sorted, place,
                                tile_expert, tile_row, n_tiles);
     return e == cudaSuccess ? launch_status() : (int)e;
 }
@@ -529,13 +554,22 @@ ZLM_EXPORT int zlm_moe_gather(const void* x, int dtype, long x_stride, const int
     return e == cudaSuccess ? launch_status() : (int)e;
 }
 
-// place: null when row p of y is pair p; else y is in grouped order and place[p] is pair p's row.
-ZLM_EXPORT int zlm_moe_combine(const float* y, const float* weights, const int* place, float* out, int T, int d, int top,
-                               int accumulate, cudaStream_t stream) {
+// place: null when row p of y is pair p; else y is in grouped order and place[p] is pair p's row.  ids (with n_real,
+// h, h_dtype, h_stride): the pairs of identity experts add the token's row of h.  shared / gate / gate_stride: an
+// output for every token, added times the sigmoid of one number a token.
+ZLM_EXPORT int zlm_moe_combine(const float* y, const float* weights, const int* place, const int* ids, int n_real,
+                               const void* h, int h_dtype, long h_stride, const float* shared, const float* gate,
+                               long gate_stride, float* out, int T, int d, int top, int accumulate, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (d <= 0 || top <= 0) return ZLM_ERR_BAD_ARG;
+    if (d <= 0 || top <= 0 || (ids != nullptr && h == nullptr)) return ZLM_ERR_BAD_ARG;
     const long total = (long)T * d;
-    cudaError_t e = launch_pdl(combine_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, y, weights, place,
-                               out, total, d, top, accumulate);
+    cudaError_t e;
+    if (h_dtype == ZLM_BF16 && ids != nullptr)
+        e = launch_pdl(combine_kernel<__nv_bfloat16>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, y, weights,
+                       place, ids, n_real, (const __nv_bfloat16*)h, h_stride, shared, gate, gate_stride, out, total, d, top,
+                       accumulate);
+    else
+        e = launch_pdl(combine_kernel<float>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, y, weights, place,
+                       ids, n_real, (const float*)h, h_stride, shared, gate, gate_stride, out, total, d, top, accumulate);
     return e == cudaSuccess ? launch_status() : (int)e;
 }

@@ -27,12 +27,14 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+
 // u[t, c] for every token of the step; reads the inputs before the step from the sequence's state.
 template <typename T>
 __global__ void conv_kernel(const T* __restrict__ x, long x_stride, const float* __restrict__ taps,
                             const float* __restrict__ bias, const float* __restrict__ state, long state_stride,
                             const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens,
-                            const int* __restrict__ slots, T* __restrict__ u, int n_tokens, int C, int K) {
+                            const int* __restrict__ slots, T* __restrict__ u, int n_tokens, int C, int K, int act) {
     pdl_launch_dependents();
     pdl_wait();
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -47,6 +49,7 @@ __global__ void conv_kernel(const T* __restrict__ x, long x_stride, const float*
                                       : st[(long)(K - 1 + i - j) * C + c];
         acc = fmaf(taps[(long)(K - 1 - j) * C + c], xv, acc);
     }
+    if (act == 1) acc = silu_f(round_to<T>(acc));       // the convolution's sum is rounded as a result of its own
     u[idx] = from_float<T>(acc);
 }
 
@@ -55,7 +58,8 @@ __global__ void conv_kernel(const T* __restrict__ x, long x_stride, const float*
 __global__ void conv_vec_kernel(const __nv_bfloat16* __restrict__ x, long x_stride, const float* __restrict__ taps,
                                 const float* __restrict__ bias, const float* __restrict__ state, long state_stride,
                                 const int* __restrict__ seq_of_token, const int* __restrict__ cu_seqlens,
-                                const int* __restrict__ slots, __nv_bfloat16* __restrict__ u, int n_tokens, int C, int K) {
+                                const int* __restrict__ slots, __nv_bfloat16* __restrict__ u, int n_tokens, int C, int K,
+                                int act) {
     pdl_launch_dependents();
     pdl_wait();
     const int groups = C / 8;
@@ -88,6 +92,10 @@ __global__ void conv_vec_kernel(const __nv_bfloat16* __restrict__ x, long x_stri
         const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] = fmaf(wv[e], xv[e], acc[e]);
+    }
+    if (act == 1) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = silu_f(round_to<__nv_bfloat16>(acc[e]));
     }
     uint4 o;
     __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
@@ -162,16 +170,123 @@ scan_kernel(const T* __restrict__ u, const float* __restrict__ gates, int gate_b
     }
 }
 
+// ------------------------------------------------------------------ selective scan
+// Per channel c with N states (the recurrence of a selective state-space layer):
+//   dt_t      = softplus(dtp[t, c])                                    (dtp: the step-size projection with its bias)
+//   S_t[n]    = exp(dt_t A[c, n]) S_(t-1)[n] + dt_t u[t, c] B_t[n]     (A < 0; B_t, C_t: N numbers a token)
+//   y_t       = sum_n S_t[n] C_t[n] + D[c] u[t, c];   out[t, c] = y_t * silu(z[t, c])
+// What a sequence carries is float [K - 1 + N, C]: rows 0..K-2 the last K-1 inputs of the convolution before the
+// scan (oldest first), row K-1+n the states S[n] of all channels.  Step sizes, decays, products and states are
+// float in both precisions.  A block takes one sequence and SS_CH channels and cuts the sequence's tokens of the
+// step into chunks; the map of a chunk on a state is S -> exp(A sum dt) S + Q, so a chunk's first pass sums its
+// step sizes and composes Q, the maps are folded in order to give each chunk its incoming states, and a second
+// pass writes the outputs.  A step of one token a sequence is one chunk and one pass.
+constexpr int SS_CH = 32;           // channels a block takes
+constexpr int SS_MAX_CHUNKS = 8;
+constexpr int SS_MAX_N = 256;       // states a channel, when their number is not one the kernel is compiled for
+
+template <typename T, int NS>
+__global__ void __launch_bounds__(SS_CH * SS_MAX_CHUNKS)
+selective_scan_kernel(const T* __restrict__ u, const float* __restrict__ dtp, const T* __restrict__ bc, long bc_stride,
+                      int b_off, int c_off, const T* __restrict__ z, long z_stride, const T* __restrict__ x,
+                      long x_stride, const float* __restrict__ a_t, const float* __restrict__ dvec,
+                      float* __restrict__ state, long state_stride, const int* __restrict__ cu_seqlens,
+                      const int* __restrict__ slots, T* __restrict__ out, int C, int N_rt, int K) {
+    extern __shared__ float ss_sm[];
+    constexpr int NA = NS > 0 ? NS : SS_MAX_N;
+    const int N = NS > 0 ? NS : N_rt;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.x;
+    const int c = blockIdx.y * SS_CH + threadIdx.x;
+    const int chunk = threadIdx.y, n_chunks = blockDim.y;
+    float* agg_q = ss_sm;                                   // [n_chunks][N][SS_CH]
+    float* agg_dt = ss_sm + (long)n_chunks * N * SS_CH;     // [n_chunks][SS_CH]
+    const int first = cu_seqlens[b], n_new = cu_seqlens[b + 1] - first;
+    const int per = (n_new + n_chunks - 1) / n_chunks;
+    const int lo = first + min(n_new, chunk * per), hi = first + min(n_new, (chunk + 1) * per);
+    const bool live = c < C;
+    float* st = state + (long)slots[b] * state_stride;
+    float A[NA], S[NA];
+    if (live) {
+#pragma unroll (NS > 0 ? NS : 1)
+        for (int n = 0; n < N; ++n)
+            A[n] = a_t[(long)n * C + c];
+    }
+    if (n_chunks > 1) {
+        // pass 1: the chunk's map on every state
+        float dt_sum = 0.f;
+        if (live) {
+#pragma unroll (NS > 0 ? NS : 1)
+            for (int n = 0; n < N; ++n) S[n] = 0.f;
+            for (int t = lo; t < hi; ++t) {
+                const float dt = softplus_f(dtp[(long)t * C + c]);
+                const float dx = dt * to_float(u[(long)t * C + c]);
+                const T* bt = bc + (long)t * bc_stride + b_off;
+                dt_sum += dt;
+#pragma unroll (NS > 0 ? NS : 1)
+                for (int n = 0; n < N; ++n)
+                    S[n] = fmaf(expf(dt * A[n]), S[n], dx * to_float(bt[n]));
+            }
+#pragma unroll (NS > 0 ? NS : 1)
+            for (int n = 0; n < N; ++n)
+                agg_q[((long)chunk * N + n) * SS_CH + threadIdx.x] = S[n];
+            agg_dt[chunk * SS_CH + threadIdx.x] = dt_sum;
+        }
+        __syncthreads();
+    }
+    if (!live) return;
+    // the states that enter this chunk: the earlier chunks' maps applied in order to the carried states
+#pragma unroll (NS > 0 ? NS : 1)
+    for (int n = 0; n < N; ++n)
+        S[n] = st[(long)(K - 1 + n) * C + c];
+    for (int j = 0; j < chunk; ++j) {
+        const float ds = agg_dt[j * SS_CH + threadIdx.x];
+#pragma unroll (NS > 0 ? NS : 1)
+        for (int n = 0; n < N; ++n)
+            S[n] = fmaf(expf(ds * A[n]), S[n], agg_q[((long)j * N + n) * SS_CH + threadIdx.x]);
+    }
+    // pass 2: the outputs
+    const float dc = dvec[c];
+    for (int t = lo; t < hi; ++t) {
+        const float dt = softplus_f(dtp[(long)t * C + c]);
+        const float uv = to_float(u[(long)t * C + c]);
+        const float dx = dt * uv;
+        const T* bt = bc + (long)t * bc_stride + b_off;
+        const T* ct = bc + (long)t * bc_stride + c_off;
+        float y = 0.f;
+#pragma unroll (NS > 0 ? NS : 1)
+        for (int n = 0; n < N; ++n)
+            {
+                S[n] = fmaf(expf(dt * A[n]), S[n], dx * to_float(bt[n]));
+                y = fmaf(S[n], to_float(ct[n]), y);
+            }
+        y = fmaf(dc, uv, y);
+        out[(long)t * C + c] = from_float<T>(y * silu_f(to_float(z[(long)t * z_stride + c])));
+    }
+    if (chunk != n_chunks - 1) return;
+    // the last chunk leaves the states after the last token, and the convolution's last K-1 inputs (rows in
+    // ascending order: row j takes what row j + n_new held, which is overwritten only later)
+#pragma unroll (NS > 0 ? NS : 1)
+    for (int n = 0; n < N; ++n)
+        st[(long)(K - 1 + n) * C + c] = S[n];
+    for (int j = 0; j < K - 1; ++j) {
+        const int i = n_new - (K - 1) + j;           // index among the step's tokens, negative: an older input
+        st[(long)j * C + c] = i >= 0 ? to_float(x[(long)(first + i) * x_stride + c]) : st[(long)(j + n_new) * C + c];
+    }
+}
+
 }  // namespace zlm
 
 using namespace zlm;
 
 // x: [T, C] rows with stride x_stride (the convolution's inputs); taps: float [K, C], the row of the current
 // token last; bias: float [C];
-// state: float [slots, K, C]; u: [T, C] contiguous.
+// state: float [slots, rows, C], of which rows 0..K-2 are the inputs before the step; u: [T, C] contiguous.
+// act: 0 none, 1 silu on the convolution's output.
 ZLM_EXPORT int zlm_causal_conv(const void* x, int dtype, long x_stride, const float* taps, const float* bias,
                                const float* state, long state_stride, const int* seq_of_token, const int* cu_seqlens,
-                               const int* slots, void* u, int n_tokens, int C, int K, cudaStream_t stream) {
+                               const int* slots, void* u, int n_tokens, int C, int K, int act, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (C <= 0 || K <= 0) return ZLM_ERR_BAD_ARG;
     const long total = (long)n_tokens * C;
@@ -179,14 +294,15 @@ ZLM_EXPORT int zlm_causal_conv(const void* x, int dtype, long x_stride, const fl
     cudaError_t e;
     if (dtype == ZLM_F32)
         e = launch_pdl(conv_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)x, x_stride, taps, bias, state,
-                       state_stride, seq_of_token, cu_seqlens, slots, (float*)u, n_tokens, C, K);
+                       state_stride, seq_of_token, cu_seqlens, slots, (float*)u, n_tokens, C, K, act);
     else if (dtype == ZLM_BF16 && C % 8 == 0 && x_stride % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)u % 16 == 0)
         e = launch_pdl(conv_vec_kernel, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, stream,
                        (const __nv_bfloat16*)x, x_stride, taps, bias, state, state_stride, seq_of_token, cu_seqlens, slots,
-                       (__nv_bfloat16*)u, n_tokens, C, K);
+                       (__nv_bfloat16*)u, n_tokens, C, K, act);
     else if (dtype == ZLM_BF16)
         e = launch_pdl(conv_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)x, x_stride,
-                       taps, bias, state, state_stride, seq_of_token, cu_seqlens, slots, (__nv_bfloat16*)u, n_tokens, C, K);
+                       taps, bias, state, state_stride, seq_of_token, cu_seqlens, slots, (__nv_bfloat16*)u, n_tokens, C, K,
+                       act);
     else
         return ZLM_ERR_UNSUPPORTED;
     return e == cudaSuccess ? launch_status() : (int)e;
@@ -219,5 +335,45 @@ ZLM_EXPORT int zlm_gated_scan(const void* u, int dtype, const float* gates, int 
                        state_stride, cu_seqlens, slots, (__nv_bfloat16*)out, C, K);
     else
         return ZLM_ERR_UNSUPPORTED;
+    return e == cudaSuccess ? launch_status() : (int)e;
+}
+
+// u: [T, C] contiguous (the convolution's output); dtp: float [T, C], the step-size projection with its bias, before
+// the softplus; bc: rows with stride bc_stride that hold B_t at b_off and C_t at c_off (N numbers each); z, x: [T, C]
+// rows with strides (the gate, and the convolution's inputs, which the state keeps); a_t: float [N, C], A transposed;
+// dvec: float [C]; state: float [slots, K - 1 + N, C]; out: [T, C] contiguous; max_new: the most tokens a sequence
+// brings (sizes the chunks).
+ZLM_EXPORT int zlm_selective_scan(const void* u, int dtype, const float* dtp, const void* bc, long bc_stride, int b_off,
+                                  int c_off, const void* z, long z_stride, const void* x, long x_stride,
+                                  const float* a_t, const float* dvec, float* state, long state_stride,
+                                  const int* cu_seqlens, const int* slots, void* out, int n_seqs, int max_new, int C,
+                                  int N, int K, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (C <= 0 || N <= 0 || K <= 0 || max_new <= 0 || b_off < 0 || c_off < 0) return ZLM_ERR_BAD_ARG;
+    if (N > SS_MAX_N || (C + SS_CH - 1) / SS_CH > 65535) return ZLM_ERR_UNSUPPORTED;
+    int chunks = (max_new + 15) / 16;                 // a chunk of fewer than 16 tokens is not worth a thread
+    if (chunks > SS_MAX_CHUNKS) chunks = SS_MAX_CHUNKS;
+    while (chunks > 1 && (size_t)chunks * (N + 1) * SS_CH * sizeof(float) > 48 * 1024) --chunks;
+    const size_t smem = chunks > 1 ? (size_t)chunks * (N + 1) * SS_CH * sizeof(float) : 0;
+    dim3 grid(n_seqs, (C + SS_CH - 1) / SS_CH), block(SS_CH, chunks);
+    cudaError_t e;
+#define ZLM_SS(TT, NS)                                                                                                \
+    e = launch_pdl(selective_scan_kernel<TT, NS>, grid, block, smem, stream, (const TT*)u, dtp, (const TT*)bc, bc_stride, \
+                   b_off, c_off, (const TT*)z, z_stride, (const TT*)x, x_stride, a_t, dvec, state, state_stride, cu_seqlens, \
+                   slots, (TT*)out, C, N, K)
+#define ZLM_SS_N(TT)                                                                                                  \
+    switch (N) {                                                                                                      \
+        case 8: ZLM_SS(TT, 8); break;                                                                                 \
+        case 16: ZLM_SS(TT, 16); break;                                                                               \
+        case 24: ZLM_SS(TT, 24); break;                                                                               \
+        case 32: ZLM_SS(TT, 32); break;                                                                               \
+        case 64: ZLM_SS(TT, 64); break;                                                                               \
+        default: ZLM_SS(TT, 0); break;                                                                                \
+    }
+    if (dtype == ZLM_F32) { ZLM_SS_N(float) }
+    else if (dtype == ZLM_BF16) { ZLM_SS_N(__nv_bfloat16) }
+    else return ZLM_ERR_UNSUPPORTED;
+#undef ZLM_SS_N
+#undef ZLM_SS
     return e == cudaSuccess ? launch_status() : (int)e;
 }

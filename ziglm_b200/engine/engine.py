@@ -293,7 +293,7 @@ class Engine:
         one entry of its block table, as long as no group lets pages go behind a window and no sequence
         reaches its limit."""
         self._repeat = None
-        if not plain_want or any(g.pages.window is not None for g in self.cache.groups):
+        if not plain_want or any(g.pages.window is not None or g.pages.chunk is not None for g in self.cache.groups):
             return
         lengths = np.array([self.cache.slots.length_of(s) for s in slots], dtype=np.int64)
         left = self.max_seq_len - int(lengths.max())

@@ -59,6 +59,8 @@ _PROTOTYPES = {
                               c_int, c_int, c_int, c_void_p],
         "zlm_norm_add_scaled": [c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_int,
                                 c_void_p],
+        "zlm_sum_norm": [c_void_p, c_void_p, c_int, c_float, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_int,
+                         c_void_p],
         "zlm_unary_act": [c_void_p, c_void_p, c_int, c_long, c_int, c_void_p],
         "zlm_sigmoid_mul": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_void_p],
         "zlm_add_row": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -66,6 +68,8 @@ _PROTOTYPES = {
         "zlm_gate_heads": [c_void_p, c_long, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int, c_float, c_void_p],
         "zlm_norm_gate": [c_void_p, c_long, c_void_p, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_float,
                           c_float, c_void_p],
+        "zlm_head_norm_gate": [c_void_p, c_long, c_void_p, c_void_p, c_long, c_void_p, c_long, c_int, c_int, c_int, c_int,
+                               c_float, c_int, c_float, c_void_p],
         "zlm_scale": [c_void_p, c_long, c_float, c_void_p],
         "zlm_add": [c_void_p, c_void_p, c_long, c_void_p],
         "zlm_convert": [c_void_p, c_int, c_void_p, c_int, c_long, c_void_p],
@@ -77,7 +81,10 @@ _PROTOTYPES = {
     },
     "recurrent": {
         "zlm_causal_conv": [c_void_p, c_int, c_long, c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p,
-                            c_void_p, c_int, c_int, c_int, c_void_p],
+                            c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "zlm_selective_scan": [c_void_p, c_int, c_void_p, c_void_p, c_long, c_int, c_int, c_void_p, c_long, c_void_p, c_long,
+                               c_void_p, c_void_p, c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_int, c_int, c_void_p],
         "zlm_gated_scan": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_long, c_void_p, c_long, c_void_p, c_float,
                            c_void_p, c_long, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
@@ -85,19 +92,23 @@ _PROTOTYPES = {
         "zlm_linear_attention_chunk": [],
         "zlm_linear_attention_segment": [],
         "zlm_linear_attention_segments": [c_int, c_int],
+        "zlm_linear_attention_prep": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                      c_float, c_void_p, c_void_p, c_int, c_void_p],
         "zlm_decayed_linear_attention": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_long, c_void_p],
     },
     "moe": {
-        "zlm_moe_route": [c_void_p, c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                          c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "zlm_moe_route": [c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                          c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
         "zlm_moe_max_tiles_scratch": [c_int, c_int],
-        "zlm_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "zlm_moe_group": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_void_p],
         "zlm_moe_grouped": [c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_long, c_int, c_int, c_int, c_int, c_int,
                             c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_void_p],
         "zlm_moe_gather": [c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
-        "zlm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "zlm_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_long, c_void_p, c_void_p,
+                            c_long, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     },
     "gemm_generic": {
         "zlm_gemm_generic": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
@@ -107,7 +118,8 @@ _PROTOTYPES = {
         "zlm_rope_store": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                            c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_void_p],
         "zlm_rope_norm_store": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_int,
-                                c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_long, c_void_p],
+                                c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                c_int, c_long, c_void_p],
         "zlm_attention_general": [c_void_p, c_long, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
                                   c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_long,
                                   c_int, c_void_p, c_long, c_void_p],
@@ -331,6 +343,24 @@ def norm_add_scaled(branch: torch.Tensor, weight: torch.Tensor, eps: float, mult
         x.data_ptr(), _ptr(h), code(h.dtype) if h is not None else F32, n, d, _stream()), "norm_add_scaled")
 
 
+def sum_norm(branch: torch.Tensor, weight: torch.Tensor, eps: float, alpha: float, x: torch.Tensor,
+             h: Optional[torch.Tensor] = None, weight_offset: float = 0.0) -> None:
+    """x = s / sqrt(mean(s^2) + eps) * (weight + weight_offset) with s = alpha * x + branch, row by row and in place,
+    and with ``h`` also h = x (the new rows, in h's type): the norm behind a sum, which norms the residual stream
+    itself.  branch and x float32 [n, d] contiguous."""
+    _cuda(branch, "branch", torch.float32); _cuda(x, "x", torch.float32); _cuda(weight, "weight")
+    n, d = x.shape
+    if branch.shape != (n, d) or weight.numel() != d:
+        raise KernelError("sum_norm: shapes do not match")
+    if h is not None:
+        _cuda(h, "h")
+        if h.shape != (n, d):
+            raise KernelError("sum_norm: h must have the shape of x")
+    _check(_fn("elementwise", "zlm_sum_norm")(
+        branch.data_ptr(), weight.data_ptr(), code(weight.dtype), float(weight_offset), float(eps), float(alpha),
+        x.data_ptr(), _ptr(h), code(h.dtype) if h is not None else F32, n, d, _stream()), "sum_norm")
+
+
 UNARY_ACTIVATIONS = {"relu2": 0, "gelu": 1}
 
 
@@ -396,6 +426,37 @@ def norm_gate(x: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor
                                                float(mult), _stream()), "norm_gate")
 
 
+HEAD_GATES = {None: 0, "sigmoid": 1, "silu": 2}
+
+
+def head_norm_gate(x: torch.Tensor, weight: Optional[torch.Tensor], gate: Optional[torch.Tensor], out: torch.Tensor,
+                   n_heads: int, eps: float, gate_kind: Optional[str] = None, mult: float = 1.0) -> None:
+    """Every head of a row normed by itself, with a gate: x float32 [T, n_heads * hd]; out[t, h, :] = x[t, h, :] /
+    sqrt(mean(x[t, h, :]^2) + eps) * weight[h, :] * act(gate[t, h, :]) * mult, in out's type.  ``weight`` (float32,
+    n_heads * hd) and ``gate`` (out's type) may be None; ``gate_kind``: "sigmoid" or "silu" (g * sigmoid(g)).
+    x, gate and out may be column slices."""
+    _rows(x, "x"); _rows(out, "out")
+    T, d = x.shape
+    if gate_kind not in HEAD_GATES:
+        raise KernelError(f"head_norm_gate: gate {gate_kind!r} is not known (sigmoid, silu)")
+    if x.dtype != torch.float32 or out.shape != (T, d) or n_heads <= 0 or d % n_heads:
+        raise KernelError("head_norm_gate: x must be float32 rows of whole heads and out of its shape")
+    if weight is not None:
+        _cuda(weight, "weight", torch.float32)
+        if weight.numel() != d:
+            raise KernelError("head_norm_gate: the weight must hold one number for each element of a row")
+    if (gate is None) != (gate_kind is None):
+        raise KernelError("head_norm_gate: a gate and its kind go together")
+    if gate is not None:
+        _rows(gate, "gate")
+        if gate.dtype != out.dtype or gate.shape != (T, d):
+            raise KernelError("head_norm_gate: the gate must have out's type and shape")
+    _check(_fn("elementwise", "zlm_head_norm_gate")(
+        x.data_ptr(), _row_stride(x), _ptr(weight), _ptr(gate), _row_stride(gate) if gate is not None else 0,
+        out.data_ptr(), _row_stride(out), code(out.dtype), T, n_heads, d // n_heads, float(eps), HEAD_GATES[gate_kind],
+        float(mult), _stream()), "head_norm_gate")
+
+
 def add_row(x: torch.Tensor, row: torch.Tensor) -> None:
     """x[t, :] += row for every t; x is float32 [T, d], row holds d elements."""
     _cuda(x, "x", torch.float32); _cuda(row, "row")
@@ -448,20 +509,51 @@ def block_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Opti
 
 
 # ------------------------------------------------------------------- recurrence
-def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor, state: torch.Tensor, step, u: torch.Tensor) -> None:
-    """u[t, c] = bias[c] + sum_j taps[K-1-j, c] * x[t-j, c] over each sequence of the step; the inputs before the
-    step are rows 0..K-2 of the sequence's state [slots, K, C] (float32; zero for a new sequence).  taps [K, C]
-    (one row per tap, the current token's last) and bias [C] are float32; x may be a column slice."""
+def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor, state: torch.Tensor, step, u: torch.Tensor,
+                activation: Optional[str] = None) -> None:
+    """u[t, c] = act(bias[c] + sum_j taps[K-1-j, c] * x[t-j, c]) over each sequence of the step; the inputs before the
+    step are rows 0..K-2 of the sequence's state [slots, rows >= K - 1, C] (float32; zero for a new sequence).  taps
+    [K, C] (one row per tap, the current token's last) and bias [C] are float32; x may be a column slice.
+    ``activation``: None or "silu"."""
     _rows(x, "x"); _cuda(u, "u", x.dtype); _cuda(taps, "taps", torch.float32); _cuda(bias, "bias", torch.float32)
     _cuda(state, "state", torch.float32)
     T, C = x.shape
     K = taps.shape[0]
-    if taps.shape != (K, C) or bias.numel() != C or u.shape != (T, C) or tuple(state.shape[1:]) != (K, C):
+    if (taps.shape != (K, C) or bias.numel() != C or u.shape != (T, C) or state.dim() != 3 or state.shape[2] != C
+            or state.shape[1] < K - 1):
         raise KernelError("causal_conv: shapes do not match")
+    if activation not in (None, "silu"):
+        raise KernelError(f"causal_conv: activation {activation!r} is not known (silu)")
     _check(_fn("recurrent", "zlm_causal_conv")(
         x.data_ptr(), code(x.dtype), _row_stride(x), taps.data_ptr(), bias.data_ptr(), state.data_ptr(), state.stride(0),
         step.seq_of_token.data_ptr(), step.cu_seqlens.data_ptr(), step.slots.data_ptr(), u.data_ptr(), T, C, K,
-        _stream()), "causal_conv")
+        1 if activation == "silu" else 0, _stream()), "causal_conv")
+
+
+def selective_scan(u: torch.Tensor, dt_pre: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int, n_states: int,
+                   z: torch.Tensor, x: torch.Tensor, a_t: torch.Tensor, d: torch.Tensor, taps: int, state: torch.Tensor,
+                   step, out: torch.Tensor) -> None:
+    """The selective scan of a state-space layer over the step's sequences.  Per channel c, with N states:
+    dt = softplus(dt_pre[t, c]); S[n] <- exp(dt A[c, n]) S[n] + dt u[t, c] B_t[n]; y = sum_n S[n] C_t[n] + d[c] u[t, c];
+    out[t, c] = y * silu(z[t, c]).  ``u`` [T, C] (the convolution's output), ``dt_pre`` float32 [T, C], B_t and C_t the
+    ``n_states`` columns of ``bc``'s rows from ``b_off`` and ``c_off`` on, ``z`` and ``x`` [T, C] (column slices
+    allowed; x: the convolution's inputs), ``a_t`` float32 [N, C] (A transposed), ``d`` float32 [C].  The state
+    [slots, taps - 1 + N, C] float32 holds the convolution's last inputs in its first taps - 1 rows and S behind them;
+    both are left as they stand after the step's last token."""
+    _cuda(u, "u"); _cuda(dt_pre, "dt_pre", torch.float32); _rows(bc, "bc"); _rows(z, "z"); _rows(x, "x")
+    _cuda(a_t, "a_t", torch.float32); _cuda(d, "d", torch.float32); _cuda(state, "state", torch.float32)
+    _cuda(out, "out", u.dtype)
+    T, C = u.shape
+    N = int(n_states)
+    if (dt_pre.shape != (T, C) or out.shape != (T, C) or z.shape != (T, C) or x.shape != (T, C) or a_t.shape != (N, C)
+            or d.numel() != C or bc.shape[0] != T or max(b_off, c_off) + N > bc.shape[1] or min(b_off, c_off) < 0
+            or tuple(state.shape[1:]) != (taps - 1 + N, C) or any(t.dtype != u.dtype for t in (bc, z, x))):
+        raise KernelError("selective_scan: shapes or types do not match")
+    _check(_fn("recurrent", "zlm_selective_scan")(
+        u.data_ptr(), code(u.dtype), dt_pre.data_ptr(), bc.data_ptr(), _row_stride(bc), int(b_off), int(c_off),
+        z.data_ptr(), _row_stride(z), x.data_ptr(), _row_stride(x), a_t.data_ptr(), d.data_ptr(), state.data_ptr(),
+        state.stride(0), step.cu_seqlens.data_ptr(), step.slots.data_ptr(), out.data_ptr(), step.n_seqs, step.max_new, C,
+        N, int(taps), _stream()), "selective_scan")
 
 
 def gated_scan(u: torch.Tensor, gates: torch.Tensor, gate_block: int, y: torch.Tensor, x: torch.Tensor,
@@ -486,35 +578,46 @@ def gated_scan(u: torch.Tensor, gates: torch.Tensor, gate_block: int, y: torch.T
 # ------------------------------------------------------------ mixture of experts
 def moe_route(z: Optional[torch.Tensor], correction: Optional[torch.Tensor], top: int, n_groups: int, keep_groups: int,
               group_best: int, ids: torch.Tensor, weights: torch.Tensor, softmax_scores=False,
-              renormalize: bool = False, h: Optional[torch.Tensor] = None, router: Optional[torch.Tensor] = None) -> None:
+              renormalize: bool = False, h: Optional[torch.Tensor] = None, router: Optional[torch.Tensor] = None,
+              weight_scale: float = 1.0, n_extra: int = 0, extra_out: Optional[torch.Tensor] = None) -> None:
     """Per token: scores = sigmoid(z) (or softmax), chosen by score + correction within the ``keep_groups`` groups
     whose ``group_best`` best choice scores sum highest; ids int32 [T, top], weights float32 [T, top] (the scores
     of the chosen, divided by their sum with ``renormalize``).  ``z``: float32 [T, E] router logits; or None with
     ``h`` [T, d] and ``router`` [E, d] of one type: the logits are then taken inside (float32 sums), which is what
     a step of few tokens wants.  ``softmax_scores`` = 2: the experts with the largest logits are chosen and their
-    weights are the softmax over the chosen logits alone (no correction, no groups)."""
+    weights are the softmax over the chosen logits alone (no correction, no groups).  The weights leave multiplied by
+    ``weight_scale``.  ``n_extra``: the last columns of ``z`` (or rows of ``router``) are not experts but further
+    products of the same rows; with ``router`` their sums are left in ``extra_out`` float32 [T, n_extra]."""
     _cuda(ids, "ids", torch.int32); _cuda(weights, "weights", torch.float32)
-    d, h_stride, h_code = 0, 0, F32
+    d, h_stride, h_code, z_stride = 0, 0, F32, 0
     if z is not None:
-        _cuda(z, "z", torch.float32)
-        T, E = z.shape
+        _rows(z, "z")
+        if z.dtype != torch.float32:
+            raise KernelError("moe_route: the logits must be float32")
+        T, E = z.shape[0], z.shape[1] - n_extra
+        z_stride = _row_stride(z)
     else:
         if h is None or router is None:
             raise KernelError("moe_route: the logits, or the rows and the router's matrix, are needed")
         _rows(h, "h"); _cuda(router, "router", h.dtype)
         T, d = h.shape
-        E = router.shape[0]
-        if router.shape != (E, d):
+        E = router.shape[0] - n_extra
+        if router.shape != (E + n_extra, d) or E <= 0:
             raise KernelError("moe_route: the router's matrix must be [E, d]")
         h_stride, h_code = _row_stride(h), code(h.dtype)
+        if n_extra:
+            _cuda(extra_out, "extra_out", torch.float32)
+            if extra_out.shape != (T, n_extra):
+                raise KernelError("moe_route: the further products go to a float32 [T, n_extra]")
     if correction is not None:
         _cuda(correction, "correction", torch.float32)
         if correction.numel() != E:
             raise KernelError("moe_route: one correction per expert is needed")
     if ids.shape != (T, top) or weights.shape != (T, top):
         raise KernelError("moe_route: ids and weights must be [T, top]")
-    _check(_fn("moe", "zlm_moe_route")(_ptr(z), _ptr(h), h_code, h_stride, _ptr(router), d, _ptr(correction), T, E, top,
-                                       n_groups, keep_groups, group_best, int(softmax_scores), int(renormalize),
+    _check(_fn("moe", "zlm_moe_route")(_ptr(z), z_stride, _ptr(h), h_code, h_stride, _ptr(router), d, _ptr(correction), T, E,
+                                       top, n_groups, keep_groups, group_best, int(softmax_scores), int(renormalize),
+                                       float(weight_scale), int(n_extra), _ptr(extra_out) if z is None else None,
                                        ids.data_ptr(), weights.data_ptr(), _stream()), "moe_route")
 
 
@@ -523,10 +626,12 @@ def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
 
 
 def moe_group(ids: torch.Tensor, n_experts: int, offs: torch.Tensor, order: torch.Tensor, place: torch.Tensor,
-              tile_expert: torch.Tensor, tile_row: torch.Tensor, n_tiles: torch.Tensor) -> None:
+              tile_expert: torch.Tensor, tile_row: torch.Tensor, n_tiles: torch.Tensor,
+              n_real: Optional[int] = None) -> None:
     """Group the (token, choice) pairs by expert: ``order`` lists the pairs expert by expert, ``place`` is its
     inverse (where pair p stands in ``order``), ``offs`` [E + 1] says where each expert's run starts, and the runs
-    are cut into tiles of rows for the grouped products."""
+    are cut into tiles of rows for the grouped products.  ``n_real``: the experts from there on are identity experts,
+    whose runs get no tiles (they have no product)."""
     for t, n in ((ids, "ids"), (offs, "offs"), (order, "order"), (place, "place"), (tile_expert, "tile_expert"),
                  (tile_row, "tile_row"), (n_tiles, "n_tiles")):
         _cuda(t, n, torch.int32)
@@ -535,7 +640,8 @@ def moe_group(ids: torch.Tensor, n_experts: int, offs: torch.Tensor, order: torc
     if (offs.numel() < n_experts + 1 or order.numel() < P or place.numel() < P or tile_expert.numel() < need
             or tile_row.numel() < need):
         raise KernelError("moe_group: an output is too short")
-    _check(_fn("moe", "zlm_moe_group")(ids.data_ptr(), P, n_experts, offs.data_ptr(), order.data_ptr(), place.data_ptr(),
+    _check(_fn("moe", "zlm_moe_group")(ids.data_ptr(), P, n_experts, n_experts if n_real is None else int(n_real),
+                                       offs.data_ptr(), order.data_ptr(), place.data_ptr(),
                                        tile_expert.data_ptr(), tile_row.data_ptr(), n_tiles.data_ptr(), _stream()),
            "moe_group")
 
@@ -597,9 +703,13 @@ def gemm_tc_groups(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, host_off
 
 
 def moe_combine(y: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, accumulate: bool,
-                place: Optional[torch.Tensor] = None) -> None:
+                place: Optional[torch.Tensor] = None, ids: Optional[torch.Tensor] = None, n_real: int = 0,
+                h: Optional[torch.Tensor] = None, shared: Optional[torch.Tensor] = None,
+                gate: Optional[torch.Tensor] = None) -> None:
     """out[t] (+)= sum_k weights[t, k] * y[row(t * top + k)], k ascending; all float32.  row(p) = p, or
-    ``place[p]`` when y is in grouped order."""
+    ``place[p]`` when y is in grouped order.  ``ids`` int32 [T, top] with ``n_real`` and ``h`` [T, d]: a pair whose
+    expert is an identity expert (ids >= n_real) adds weights[t, k] * h[t] instead.  ``shared`` float32 [T, d]: added
+    for every token, times sigmoid(gate[t]) when ``gate`` (float32, one number a token, any row stride) is given."""
     _cuda(y, "y", torch.float32); _cuda(weights, "weights", torch.float32); _cuda(out, "out", torch.float32)
     T, top = weights.shape
     d = out.shape[1]
@@ -609,8 +719,25 @@ def moe_combine(y: torch.Tensor, weights: torch.Tensor, out: torch.Tensor, accum
         _cuda(place, "place", torch.int32)
         if place.numel() < T * top:
             raise KernelError("moe_combine: one place per pair is needed")
-    _check(_fn("moe", "zlm_moe_combine")(y.data_ptr(), weights.data_ptr(), _ptr(place), out.data_ptr(), T, d, top,
-                                         int(accumulate), _stream()), "moe_combine")
+    h_code, h_stride, gate_stride = F32, 0, 0
+    if ids is not None:
+        _cuda(ids, "ids", torch.int32); _rows(h, "h")
+        if ids.numel() < T * top or h.shape != (T, d):
+            raise KernelError("moe_combine: the identity experts need every pair's expert and the tokens' rows")
+        h_code, h_stride = code(h.dtype), _row_stride(h)
+    if shared is not None:
+        _cuda(shared, "shared", torch.float32)
+        if shared.shape != (T, d):
+            raise KernelError("moe_combine: the shared output must be float32 [T, d]")
+        if gate is not None:
+            if not gate.is_cuda or gate.dtype != torch.float32 or gate.shape[0] != T:
+                raise KernelError("moe_combine: the gate must be float32 with one number a token")
+            gate_stride = gate.stride(0) if T > 1 else 1
+    elif gate is not None:
+        raise KernelError("moe_combine: a gate goes with a shared output")
+    _check(_fn("moe", "zlm_moe_combine")(y.data_ptr(), weights.data_ptr(), _ptr(place), _ptr(ids), int(n_real), _ptr(h),
+                                         h_code, h_stride, _ptr(shared), _ptr(gate), gate_stride, out.data_ptr(), T, d,
+                                         top, int(accumulate), _stream()), "moe_combine")
 
 
 def add_(y: torch.Tensor, x: torch.Tensor) -> None:
@@ -704,11 +831,15 @@ def rope_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, rotary
 def rope_norm_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, rotary_dim: int,
                     inv_freq: Optional[torch.Tensor], amplitude: float, norm_dim: int, norm_eps: float,
                     positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
-                    k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], page_size: int) -> None:
+                    k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], page_size: int,
+                    norm_first: bool = False, q_weight: Optional[torch.Tensor] = None,
+                    k_weight: Optional[torch.Tensor] = None) -> None:
     """``rope_store`` with an amplitude on the cosines and sines and a unit RMS norm behind the rotation: every
     q and k head of a row [q heads | k heads | v heads | ...] of qkv is turned, divided by
     sqrt(mean of the squares of its first ``norm_dim`` dimensions + norm_eps) (``norm_dim`` 0: not divided), written
-    back and (keys, values) stored in the cache pages.  The row may be wider than the heads."""
+    back and (keys, values) stored in the cache pages.  The row may be wider than the heads.  With ``norm_first`` the
+    norm stands before the rotation, and ``q_weight`` / ``k_weight`` (float32 [head_dim], one for all query heads and
+    one for all key heads; None: no weight) multiply the normed heads."""
     _rows(qkv, "qkv"); _cuda(positions, "positions", torch.int32); _cuda(seq_of_token, "seq_of_token", torch.int32)
     _cuda(block_table, "block_table", torch.int32)
     T = qkv.shape[0]
@@ -718,6 +849,12 @@ def rope_norm_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, r
         _cuda(inv_freq, "inv_freq", torch.float32)
         if inv_freq.numel() * 2 != rotary_dim:
             raise KernelError("rope_norm_store: the frequency table must hold rotary_dim/2 entries")
+    for w in (q_weight, k_weight):
+        if w is not None:
+            _cuda(w, "norm weight", torch.float32)
+            if not norm_first or w.numel() != head_dim:
+                raise KernelError("rope_norm_store: a norm weight holds one number for each element of a head and goes "
+                                  "with the norm before the rotation")
     page_stride = 0
     if k_pages is not None:
         _cuda(k_pages, "k_pages", qkv.dtype); _cuda(v_pages, "v_pages", qkv.dtype)
@@ -726,7 +863,8 @@ def rope_norm_store(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, r
         page_stride = k_pages.stride(0)
     _check(_fn("attention", "zlm_rope_norm_store")(
         qkv.data_ptr(), code(qkv.dtype), _row_stride(qkv), T, n_heads, n_kv, head_dim, rotary_dim, _ptr(inv_freq),
-        float(amplitude), int(norm_dim), float(norm_eps), positions.data_ptr(), seq_of_token.data_ptr(),
+        float(amplitude), int(norm_dim), float(norm_eps), int(bool(norm_first)), _ptr(q_weight), _ptr(k_weight),
+        positions.data_ptr(), seq_of_token.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), _ptr(k_pages), _ptr(v_pages), page_size, page_stride, _stream()),
         "rope_norm_store")
 
@@ -779,6 +917,31 @@ def qk_prep(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, rotary_di
 def linear_attention_chunk() -> int:
     """Tokens of a chunk of ``decayed_linear_attention``: the table of decay powers holds this many plus one a head."""
     return int(_fn("linear_attention", "zlm_linear_attention_chunk")())
+
+
+def linear_attention_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n_heads: int, dim: int, value_dim: int,
+                          rotary_dim: int, inv_freq: Optional[torch.Tensor], k_scale: float, positions: torch.Tensor,
+                          out: torch.Tensor) -> None:
+    """out (float32 [T, 2 * heads * dim + heads * value_dim], laid out [q | k | v]) = head h's q, k and v of ``proj``'s
+    rows (at q_off + h*dim, k_off + h*dim, v_off + h*value_dim), with the first ``rotary_dim`` dimensions of every q
+    and k head turned by the token's position (dimension i together with i + rotary_dim/2, angle position *
+    inv_freq[i]; ``inv_freq`` None: not turned) and k times ``k_scale``: what enters a linear-attention recurrence
+    whose q and k carry rotary positions, in float32 from the read on."""
+    _rows(proj, "proj"); _cuda(out, "out", torch.float32); _cuda(positions, "positions", torch.int32)
+    T = proj.shape[0]
+    qk, hv = n_heads * dim, n_heads * value_dim
+    if out.shape != (T, 2 * qk + hv):
+        raise KernelError("linear_attention_prep: out must be float32 [T, 2 * heads * dim + heads * value_dim]")
+    if max(q_off, k_off) + qk > proj.shape[1] or v_off + hv > proj.shape[1] or min(q_off, k_off, v_off) < 0:
+        raise KernelError("linear_attention_prep: the heads lie outside the rows")
+    if inv_freq is not None:
+        _cuda(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() * 2 != rotary_dim or rotary_dim > dim:
+            raise KernelError("linear_attention_prep: the frequency table must hold rotary_dim/2 entries")
+    _check(_fn("linear_attention", "zlm_linear_attention_prep")(
+        proj.data_ptr(), code(proj.dtype), _row_stride(proj), q_off, k_off, v_off, n_heads, dim, value_dim,
+        int(rotary_dim) if inv_freq is not None else 0, _ptr(inv_freq), float(k_scale), positions.data_ptr(),
+        out.data_ptr(), T, _stream()), "linear_attention_prep")
 
 
 def decayed_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n_heads: int, dim: int,
@@ -906,7 +1069,7 @@ def attention_decode(qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: i
             raise KernelError("attention_decode: the gates must be [T, n_heads] of the rows' type")
     status = _fn("attention_tc", "zlm_attention_decode")(
         qkv.data_ptr(), qkv.stride(0), out.data_ptr(), T, n_heads, n_kv, head_dim, scale, float(softcap or 0.0),
-        int(window or 0), int(keep_first or 0) if window else 0, _ptr(sinks), _ptr(head_gate),
+        int(window or 0), int(keep_first or 0) if (window or 0) > 0 else 0, _ptr(sinks), _ptr(head_gate),
         _row_stride(head_gate) if head_gate is not None else 0, float(head_gate_mult),
         positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(), block_table.stride(0),
         k_pages.data_ptr(), v_pages.data_ptr(), k_pages.shape[0], page_size, n_splits, part_o.data_ptr(),
@@ -1056,7 +1219,7 @@ def attention_prefill_fmha(qkv: torch.Tensor, out: torch.Tensor, n_seqs: int, ma
         raise KernelError("attention_prefill_fmha: sequence arrays are too short")
     status = _fn("attention_fmha", "zlm_attention_prefill_fmha")(
         qkv.data_ptr(), qkv.stride(0), qkv.shape[0], out.data_ptr(), n_seqs, max_new, n_heads, n_kv, head_dim, scale,
-        float(softcap or 0.0), int(window or 0), int(keep_first or 0) if window else 0, _ptr(sinks), cu_seqlens.data_ptr(),
+        float(softcap or 0.0), int(window or 0), int(keep_first or 0) if (window or 0) > 0 else 0, _ptr(sinks), cu_seqlens.data_ptr(),
         past_lens.data_ptr(), block_table.data_ptr(), block_table.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
         k_pages.shape[0], page_size, _stream())
     if status == -2:
@@ -1115,8 +1278,10 @@ def attention_with_rope(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int
 def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, scale: float,
               window: Optional[int], io, softcap: float = 0.0, gate: Optional[torch.Tensor] = None,
               keep_first: int = 0, sinks: Optional[torch.Tensor] = None, head_gate: Optional[torch.Tensor] = None,
-              head_gate_mult: float = 1.0) -> bool:
-    """Attention of a step's tokens over the cache of the running layer; picks the kernel.  ``softcap`` c > 0:
+              head_gate_mult: float = 1.0, chunk: Optional[int] = None) -> bool:
+    """Attention of a step's tokens over the cache of the running layer; picks the kernel.  ``chunk`` (instead of
+    ``window``): the positions of a sequence form chunks of that many, counted from its start, and a query sees the
+    earlier keys of its own chunk only (the kernels take it as a negative window).  ``softcap`` c > 0:
     the scaled scores become c * tanh(score / c).  ``keep_first``: with a window, the first positions of a sequence
     that stay visible behind it.  ``sinks`` (float32, one per query head): a number in the softmax's denominator that
     belongs to no key.  ``gate`` ([T, n_heads * head_dim] of the step's type): the flat
@@ -1127,14 +1292,21 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
     sequence's keys applies it where it combines the splits, and the result says so likewise."""
     if gate is not None and head_gate is not None:
         raise KernelError("attention: a gate an element or a gate a head, not both")
-    keep_first = int(keep_first or 0) if window else 0
+    if chunk:
+        if window:
+            raise KernelError("attention: a window or chunks, not both")
+        keep_first = 0
+        span = min(step.max_total, int(chunk))        # the most keys a token sees
+        window = -int(chunk)
+    else:
+        keep_first = int(keep_first or 0) if window else 0
+        span = min(step.max_total, window + keep_first) if window else step.max_total
     # kept first tokens and sinks: the tcgen05 prompt kernel and the decode kernel that splits a sequence's keys
     # know both, the other tensor-core kernels neither
     plain_only = keep_first > 0 or sinks is not None
     if plain_only and _tc_attention_ok(qkv.dtype, n_heads, n_kv, head_dim, io.page_size):
         if step.single_token:
-            n_splits = decode_splits(step.n_tokens, n_kv, min(step.max_total, window + keep_first) if window else step.max_total,
-                                     io.page_size)
+            n_splits = decode_splits(step.n_tokens, n_kv, span, io.page_size)
             part_o = step.ws.buf("attn_part_o", (step.n_tokens * n_heads * n_splits * head_dim,), torch.float32)
             part_ml = step.ws.buf("attn_part_ml", (step.n_tokens * n_heads * n_splits * 2,), torch.float32)
             if attention_decode(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions, step.seq_of_token,
@@ -1158,7 +1330,7 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
                                      n_blocks, counters, scratch, softcap=softcap, gate=gate):
                 return gate is not None
         if step.single_token:
-            n_splits = decode_splits(step.n_tokens, n_kv, step.max_total, io.page_size)
+            n_splits = decode_splits(step.n_tokens, n_kv, span, io.page_size)
             part_o = step.ws.buf("attn_part_o", (step.n_tokens * n_heads * n_splits * head_dim,), torch.float32)
             part_ml = step.ws.buf("attn_part_ml", (step.n_tokens * n_heads * n_splits * 2,), torch.float32)
             if attention_decode(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions,
@@ -1173,7 +1345,7 @@ def attention(step, qkv: torch.Tensor, out: torch.Tensor, n_heads: int, n_kv: in
                 return False
             if attention_prefill(*args, softcap=softcap):
                 return False
-    max_keys = min(step.max_total, window + keep_first) if window else step.max_total
+    max_keys = span
     need = attention_general_scratch(step.n_tokens, n_heads, n_kv, head_dim, max_keys)
     scratch = step.ws.buf("attn_parts", (need,), torch.float32) if need > 0 else None
     attention_general(qkv, out, n_heads, n_kv, head_dim, scale, window, step.positions, step.seq_of_token,

@@ -2,7 +2,7 @@ from .base import (KVNeed, LayerIO, NormedInput, ParamDecl, Part, StateNeed, blo
                    mixer_class, norm_class, position_class, register_block, register_feed_forward, register_hook,
                    register_mixer, register_norm, register_position, unregister)
 from .linear import Linear
-from . import norm, rope, attention, mlp, block, hooks, latent_attention, recurrent, moe, capped_attention, linear_attention, side_by_side  # noqa: F401  (registers the parts)
+from . import norm, rope, attention, mlp, block, hooks, latent_attention, recurrent, moe, capped_attention, linear_attention, side_by_side, selective_scan  # noqa: F401  (registers the parts)
 
 __all__ = [
     "KVNeed", "LayerIO", "ParamDecl", "Part", "StateNeed", "Linear",

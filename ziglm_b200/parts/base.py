@@ -55,12 +55,15 @@ class KVNeed:
     """Keys and values a mixer wants kept: per position n_kv_heads x head_dim, all of them or a window.
     ``values_are_keys``: one vector per position serves as key and as value (a latent both are made from), so
     only the key pages exist and ``LayerIO.v_pages`` is the same memory.  ``keep_first``: with a window, the first
-    positions of a sequence that stay visible behind it (their pages are never let go)."""
+    positions of a sequence that stay visible behind it (their pages are never let go).  ``chunk`` (instead of a
+    window): a query sees the keys of its own chunk of that many positions only, chunks counted from the start of the
+    sequence, so the pages before the running chunk are let go."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     values_are_keys: bool = False
     keep_first: int = 0
+    chunk: Optional[int] = None
 
 
 @dataclass(frozen=True)

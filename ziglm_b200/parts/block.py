@@ -289,6 +289,76 @@ class PostNormBlock(Part):
 register_block("postnorm", PostNormBlock)
 
 
+class SumNormBlock(Part):
+    """Norms behind the sums: x <- post1(alpha x + mixer(x)) and, where the layer has a feed-forward,
+    x <- post2(alpha x + ffn(x)).  The residual stream itself is normed after every sublayer, and the sublayers read it
+    as it is (its rows in the step's storage type; in float32 the residual itself).
+
+    The two norms come in ``LayerSpec.options`` (``mixer_post_norm``, ``ffn_post_norm``) and alpha as
+    ``residual_mult`` (default 1).  A sublayer writes its output into a float32 branch buffer; the norm's kernel reads
+    it, forms the sum and its norm in float32, writes the stream in place and leaves the new rows for the sublayer
+    that follows, here or in the next block.  ``mixer_norm`` is the part that makes those rows when nobody has (the
+    first block of a model, or a block behind one of another arrangement)."""
+
+    def __init__(self, spec: LayerSpec, dtype: torch.dtype, device: torch.device):
+        super().__init__(spec, dtype, device)
+        self.alpha = float(spec.options.get("residual_mult", 1.0))
+        self.mixer_norm = norm_class("cast")(None, dtype, device)
+        self.parts: Dict[str, Part] = {}
+        for prefix, klass, sub in self._children(spec):
+            self.parts[prefix] = klass(sub, dtype, device)
+        self.mixer = self.parts["mixer."]
+        self.mixer_post = self.parts["mixer_post_norm."]
+        self.ffn = self.parts.get("ffn.")
+        self.ffn_post = self.parts.get("ffn_post_norm.")
+        for post in (self.mixer_post, self.ffn_post):
+            if post is not None and not hasattr(post, "sum_normed"):
+                raise ValueError("sum_norm: the norm behind a sum must offer sum_normed")
+
+    _children = PostNormBlock._children
+    declare = PostNormBlock.declare
+    bind = PostNormBlock.bind
+    kernel_libraries = PostNormBlock.kernel_libraries
+    cache_needs = PostNormBlock.cache_needs
+    state_needs = PostNormBlock.state_needs
+
+    def accepts_normed_input(self) -> bool:
+        """The block before may hand over the rows this block's mixer reads (``h_in``)."""
+        return True
+
+    def _close(self, step, post, branch: torch.Tensor, x: torch.Tensor, want_rows: bool, name: str):
+        """x <- post(alpha x + branch); with ``want_rows`` also the new rows of x for the sublayer that follows."""
+        if not want_rows or self.dtype == torch.float32:
+            post.sum_normed(step, branch, x, self.alpha)
+            return x if want_rows else None
+        return post.sum_normed(step, branch, x, self.alpha, rows_out=step.ws.buf(name, tuple(x.shape), self.dtype))
+
+    def _run(self, part, step, io, h, x: torch.Tensor) -> torch.Tensor:
+        branch = step.ws.buf("branch", tuple(x.shape), torch.float32)
+        args = (step, h, branch) if io is None else (step, io, h, branch)
+        if part.can_overwrite:
+            part.forward(*args, accumulate=False)
+        else:
+            branch.zero_()
+            part.forward(*args)
+        return branch
+
+    def forward(self, step, io: LayerIO, x: torch.Tensor, h_in=None, next_norm=None):
+        """``h_in``: the rows the mixer reads, left by the block before.  ``next_norm``: the first part of the block
+        after; if that block reads the residual itself (its part is the cast) the result is the rows it reads."""
+        h = h_in if isinstance(h_in, torch.Tensor) else self.mixer_norm.forward(step, x, name="rows_mixer")
+        feeds_next = type(next_norm) is type(self.mixer_norm)
+        branch = self._run(self.mixer, step, io, h, x)
+        if self.ffn is None:
+            return self._close(step, self.mixer_post, branch, x, feeds_next, "rows_next")
+        h = self._close(step, self.mixer_post, branch, x, True, "rows_ffn")
+        branch = self._run(self.ffn, step, None, h, x)
+        return self._close(step, self.ffn_post, branch, x, feeds_next, "rows_next")
+
+
+register_block("sum_norm", SumNormBlock)
+
+
 class SharedNormBlock(Part):
     """One norm whose rows the mixer and the feed-forward both read: with h = norm(x), x += mixer(h) + ff(h).
 

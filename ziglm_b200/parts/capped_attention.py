@@ -7,11 +7,16 @@ For the rows h the mixer reads, H query heads, G key/value heads, query/key size
                                                 position encoding; cosines and sines times its amplitude
     q, k <- q / rms(q), k / rms(k)              per head over D, no weight        (``qk_norm`` "head": the default
                                                 when ``qk_norm_eps`` is given; None: left out)
+                                                (``qk_norm`` "head_first": per head over D BEFORE the rotation, times a
+                                                weight of D numbers that all query heads share, and one for the keys)
     v <- (1 - l) v + l v_first                  v_first: the values of the same tokens in the first layer that takes
                                                 part (``value_mix`` "mix"; that layer itself says "first"); l learned
     s_ij = (q_i . k_j) * scale;  s <- c tanh(s / c)                               (``softcap`` c; None: left out)
     j visible to i:  j <= i and (i - j < window or j < keep_first)                (``MixerSpec.window``, ``keep_first``)
-    p = softmax over the visible j, with exp(sink_h) also in the denominator       (``sink``: a learned number a head)
+                     or j <= i and floor(i / c) = floor(j / c)                    (``chunk`` c instead of a window)
+    p = softmax over the visible j, with exp(sink_h) also in the denominator       (``sink``: a learned number a head;
+                                                                                  "zero": the fixed number 0, so that
+                                                                                  the denominator holds one more 1)
     o_i = sum_j p_ij v_j
     out = W_o (concat(o) * sigmoid(W_g h))      one gate an element (``gate`` "sigmoid") or one a head
                                                 (``gate`` "sigmoid_head", times ``out_scale``); None: left out
@@ -72,8 +77,8 @@ class CappedAttention(Part):
         self.softcap = float(o["softcap"]) if o.get("softcap") else 0.0
         self.norm_eps = None if o.get("qk_norm_eps") is None else float(o["qk_norm_eps"])
         self.norm_kind = None if self.norm_eps is None else o.get("qk_norm", "head")
-        if self.norm_kind not in (None, "head", "whole"):
-            raise ValueError(f"capped_attention: norm of q and k {self.norm_kind!r} is not known (head, whole)")
+        if self.norm_kind not in (None, "head", "whole", "head_first"):
+            raise ValueError(f"capped_attention: norm of q and k {self.norm_kind!r} is not known (head, whole, head_first)")
         self.gate = o.get("gate")
         if self.gate not in (None, "sigmoid", "sigmoid_head"):
             raise ValueError(f"capped_attention: output gate {self.gate!r} is not known (sigmoid, sigmoid_head)")
@@ -83,7 +88,13 @@ class CappedAttention(Part):
             raise ValueError("capped_attention: a factor on the output rides on the gate of a head (sigmoid_head)")
         self.window = None if spec.window is None else int(spec.window)
         self.keep_first = int(o.get("keep_first") or 0) if self.window is not None else 0
+        self.chunk = None if o.get("chunk") is None else int(o["chunk"])
+        if self.chunk is not None and (self.chunk <= 0 or self.window is not None):
+            raise ValueError("capped_attention: chunks have a positive size and do not go with a window")
+        if o.get("sink") not in (None, False, True, "zero"):
+            raise ValueError(f"capped_attention: sink {o.get('sink')!r} is not known (true, \"zero\")")
         self.has_sink = bool(o.get("sink"))
+        self.sink_learned = o.get("sink") is True
         self.value_mix = o.get("value_mix")
         if self.value_mix not in (None, "first", "mix"):
             raise ValueError(f"capped_attention: value_mix {self.value_mix!r} is not known (first, mix)")
@@ -129,7 +140,10 @@ class CappedAttention(Part):
         if o.get("qk_norm_eps") is not None and o.get("qk_norm") == "whole":
             p["q_norm.weight"] = ParamDecl((H * D,), init="ones")
             p["k_norm.weight"] = ParamDecl((G * D,), init="ones")
-        if o.get("sink"):
+        if o.get("qk_norm_eps") is not None and o.get("qk_norm") == "head_first":
+            p["q_norm.weight"] = ParamDecl((D,), init="ones")
+            p["k_norm.weight"] = ParamDecl((D,), init="ones")
+        if o.get("sink") is True:
             p["sink"] = ParamDecl((H,))
         if o.get("value_mix") is not None:
             p["vmix"] = ParamDecl(())        # the layer that only leaves its values owns one too, and does not use it
@@ -167,8 +181,12 @@ class CappedAttention(Part):
         if self.norm_kind == "whole":
             self.q_norm_w = _pad_heads(_order_heads(tensors["q_norm.weight"].float(), H, D, order), H, D, P).contiguous()
             self.k_norm_w = _pad_heads(_order_heads(tensors["k_norm.weight"].float(), G, D, order), G, D, P).contiguous()
+        if self.norm_kind == "head_first":
+            self.q_norm_w = _pad_heads(_order_heads(tensors["q_norm.weight"].float(), 1, D, order), 1, D, P).contiguous()
+            self.k_norm_w = _pad_heads(_order_heads(tensors["k_norm.weight"].float(), 1, D, order), 1, D, P).contiguous()
         if self.has_sink:
-            self.sinks = tensors["sink"].float().contiguous()
+            self.sinks = (tensors["sink"].float().contiguous() if self.sink_learned
+                          else torch.zeros(H, dtype=torch.float32, device=w_o.device))
         if self.value_mix == "mix":
             self.mix = float(tensors["vmix"].float().item())
 
@@ -182,7 +200,7 @@ class CappedAttention(Part):
         return libs
 
     def cache_needs(self) -> Optional[KVNeed]:
-        return KVNeed(self.n_kv, self.kept, self.window, keep_first=self.keep_first)
+        return KVNeed(self.n_kv, self.kept, self.window, keep_first=self.keep_first, chunk=self.chunk)
 
     def state_needs(self) -> Optional[StateNeed]:
         return None
@@ -210,10 +228,12 @@ class CappedAttention(Part):
                             {None: 0, "first": 1, "mix": 2}[self.value_mix], self.mix, mix_buf, self.value_dim,
                             step.positions, step.seq_of_token, io.block_table, k_pages, v_pages, io.page_size)
         else:
-            head_norm = self.norm_kind == "head"
+            head_norm = self.norm_kind in ("head", "head_first")
+            first = self.norm_kind == "head_first"
             kernels.rope_norm_store(proj, H, G, P, rot, inv_freq, amplitude, self.dim if head_norm else 0,
                                     (self.norm_eps or 0.0) if head_norm else 0.0, step.positions, step.seq_of_token,
-                                    io.block_table, k_pages, v_pages, io.page_size)
+                                    io.block_table, k_pages, v_pages, io.page_size, norm_first=first,
+                                    q_weight=self.q_norm_w if first else None, k_weight=self.k_norm_w if first else None)
         out = step.ws.buf("attn_out", (T, H * P), self.dtype)
         gate = proj[:, heads_width:] if self.gate == "sigmoid" else None
         # the flat decode kernel multiplies by an element gate's sigmoid as it stores, the decode kernel that splits a
@@ -221,7 +241,7 @@ class CappedAttention(Part):
         head_gate = proj[:, heads_width:heads_width + H] if self.gate == "sigmoid_head" else None
         gated = kernels.attention(step, proj, out, H, G, P, self.scale, self.window, io, softcap=self.softcap, gate=gate,
                                   keep_first=self.keep_first, sinks=self.sinks, head_gate=head_gate,
-                                  head_gate_mult=self.out_scale)
+                                  head_gate_mult=self.out_scale, chunk=self.chunk)
         if self.gate == "sigmoid" and not gated:
             kernels.sigmoid_mul(out, gate, out)
         elif self.gate == "sigmoid_head" and not gated:

@@ -5,6 +5,11 @@ For the rows h the mixer reads, H heads of query/key size D and value size V, de
     S_t = a_h S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t          S: [D, V] per head, zero where a sequence starts
     out = W_o (norm(concat(o)) * sigmoid(W_g h) * out_scale)   the heads RMS-normed together with a weight
                                                               (``gate`` None: without the sigmoid)
+Options beside these: ``MixerSpec.position`` (rotary positions on q and k: the first rotated dimensions of every
+head are turned before the recurrence), ``key_scale`` (k times a factor, after the rotation), ``norm`` "heads" (the
+default: the heads normed together with the weight ``norm.weight``) or "head" (every head divided by its own root
+mean square, no weight), ``gate`` "sigmoid", "silu" (g * sigmoid(g)) or None.  With a rotation or a factor on k the
+rotated q, the rotated and scaled k and v go to the recurrence as float32 rows made by one kernel.
 There is no other factor on the scores and no softmax.  A sequence carries [H, D, V] float32 from step to step
 (``StateNeed``); the recurrence, the scores q . k with their decays and the outputs are float32 in both precisions
 (the kernel works through a step in chunks of tokens, a decoded token being a chunk of one).  The four projections of
@@ -18,7 +23,7 @@ import torch
 
 from .. import kernels
 from ..config.spec import MixerSpec
-from .base import KVNeed, LayerIO, ParamDecl, Part, StateNeed, register_mixer
+from .base import KVNeed, LayerIO, ParamDecl, Part, StateNeed, position_class, register_mixer
 from .linear import Linear
 
 
@@ -39,8 +44,20 @@ class DecayedLinearAttention(Part):
         if self.activation not in (None, "silu"):
             raise ValueError(f"decayed_linear_attention: activation {self.activation!r} is not known (silu)")
         self.gate = o.get("gate")
-        if self.gate not in (None, "sigmoid"):
-            raise ValueError(f"decayed_linear_attention: output gate {self.gate!r} is not known (sigmoid)")
+        if self.gate not in (None, "sigmoid", "silu"):
+            raise ValueError(f"decayed_linear_attention: output gate {self.gate!r} is not known (sigmoid, silu)")
+        self.norm_kind = o.get("norm", "heads")
+        if self.norm_kind not in ("heads", "head"):
+            raise ValueError(f"decayed_linear_attention: norm {self.norm_kind!r} is not known (heads, head)")
+        self.key_scale = float(o.get("key_scale", 1.0))
+        self.position = position_class(spec.position.kind)(spec.position, dtype, device)
+        table = self.position.rotary_table()
+        if table is not None and getattr(self.position, "head_order", lambda d: None)(self.dim) is not None:
+            raise ValueError("decayed_linear_attention: rotary positions turn the halves of a head's rotated part")
+        self.prepared = table is not None or self.key_scale != 1.0
+        if self.prepared and self.activation is not None:
+            raise ValueError("decayed_linear_attention: an activation on q, k and v is not combined with a rotation "
+                             "or a factor on k")
         self.eps = float(o["norm_eps"])
         self.out_scale = float(o.get("out_scale", 1.0))
         self.proj: Optional[Linear] = None       # [q; k; v; g]
@@ -53,8 +70,10 @@ class DecayedLinearAttention(Part):
         H, D, d = spec.n_heads, spec.head_dim, spec.width
         V = int(spec.options.get("value_dim", D))
         p = {"q.weight": ParamDecl((H * D, d)), "k.weight": ParamDecl((H * D, d)), "v.weight": ParamDecl((H * V, d)),
-             "norm.weight": ParamDecl((H * V,), init="ones"), "o.weight": ParamDecl((d, H * V))}
-        if spec.options.get("gate") == "sigmoid":
+             "o.weight": ParamDecl((d, H * V))}
+        if spec.options.get("norm", "heads") == "heads":
+            p["norm.weight"] = ParamDecl((H * V,), init="ones")
+        if spec.options.get("gate") is not None:
             p["g.weight"] = ParamDecl((H * V, d))
         return p
 
@@ -64,10 +83,10 @@ class DecayedLinearAttention(Part):
         wide = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
         self.proj = Linear(torch.cat([w.to(wide) for w in ws], dim=0))
         self.o = Linear(tensors["o.weight"])
-        self.norm_w = tensors["norm.weight"].float().contiguous()
+        self.norm_w = tensors["norm.weight"].float().contiguous() if self.norm_kind == "heads" else None
         chunk = kernels.linear_attention_chunk()
         table = torch.tensor([[a ** n for n in range(chunk + 1)] for a in self.decay], dtype=torch.float64)
-        self.pows = table.to(torch.float32).to(self.norm_w.device).contiguous()
+        self.pows = table.to(torch.float32).to(self.o.weight.device).contiguous()
 
     def kernel_libraries(self) -> Tuple[str, ...]:
         libs = ("linear_attention", "elementwise")
@@ -89,9 +108,21 @@ class DecayedLinearAttention(Part):
         proj = step.ws.buf("lin_proj", (T, 2 * qk + hv + (hv if self.gate else 0)), self.dtype)
         self.proj(h, proj)
         mixed = step.ws.buf("lin_mixed", (T, hv), torch.float32)
-        kernels.decayed_linear_attention(proj, 0, qk, 2 * qk, H, D, V, self.activation, self.pows, io.state, step, mixed)
+        rows = proj
+        if self.prepared:
+            # rotated q, rotated and scaled k, and v as float32 rows: nothing that enters the recurrence is rounded again
+            rows = step.ws.buf("lin_prepared", (T, 2 * qk + hv), torch.float32)
+            table = self.position.rotary_table()
+            inv_freq, rot = table if table is not None else (None, 0)
+            kernels.linear_attention_prep(proj, 0, qk, 2 * qk, H, D, V, rot, inv_freq, self.key_scale, step.positions, rows)
+        kernels.decayed_linear_attention(rows, 0, qk, 2 * qk, H, D, V, self.activation, self.pows, io.state, step, mixed)
         out = step.ws.buf("lin_out", (T, hv), self.dtype)
-        kernels.norm_gate(mixed, self.norm_w, proj[:, 2 * qk + hv:] if self.gate else None, out, self.eps, self.out_scale)
+        gate = proj[:, 2 * qk + hv:] if self.gate else None
+        if self.norm_kind == "heads" and self.gate != "silu":
+            kernels.norm_gate(mixed, self.norm_w, gate, out, self.eps, self.out_scale)
+        else:
+            kernels.head_norm_gate(mixed, self.norm_w, gate, out, 1 if self.norm_kind == "heads" else H, self.eps,
+                                   self.gate, self.out_scale)
         self.o(out, residual, accumulate=accumulate)
         return None
 

@@ -10,7 +10,11 @@ the largest logits, weighted by the softmax over the chosen logits alone), ``cor
 per expert enters the choice), ``renormalize``.  The experts' activation is silu(gate) * up, or with
 ``activation`` "swish_clamped" and the options ``limit`` and ``slope`` the clamped form
 min(g, L) sigmoid(slope min(g, L)) (clamp(u, -L, L) + 1).  ``shared``: the spec of a feed-forward that runs for
-every token and is added to the experts' sum (its tensors under ``shared.``).
+every token and is added to the experts' sum (its tensors under ``shared.``); with ``shared_gate`` it is added times
+sigmoid(w_sg . h), one number a token (the tensor ``shared_gate.weight`` [1, d], whose product rides on the router's).
+``identity``: that many further outputs of the router, behind the experts', stand for identity experts, which have no
+tensors and whose output is the token's row h itself (times the weight); scores, offsets, groups and the choice run
+over experts and identity experts together.  ``weight_scale``: a factor on the chosen experts' weights.
 
 The (token, choice) pairs are grouped by expert on the device (nothing is read back, so a decode step stays a
 replayable graph), the experts' products run over the groups, each pair's result lands in a float32 row of its
@@ -35,6 +39,14 @@ class MixtureOfExperts(Part):
         super().__init__(spec, dtype, device)
         o = spec.options
         self.n_experts, self.top = int(o["experts"]), int(o["top"])
+        self.identity = int(o.get("identity") or 0)
+        if self.identity < 0:
+            raise ValueError("moe: the number of identity experts cannot be negative")
+        self.n_routed = self.n_experts + self.identity       # outputs of the router
+        self.weight_scale = float(o.get("weight_scale", 1.0))
+        self.shared_gate = bool(o.get("shared_gate", False))
+        if self.shared_gate and o.get("shared") is None:
+            raise ValueError("moe: a gate on the shared expert needs a shared expert")
         self.groups, self.keep_groups = int(o.get("groups", 1)), int(o.get("keep_groups", o.get("groups", 1)))
         self.group_best = int(o.get("group_best", 2))
         if o.get("score", "sigmoid") not in self.SCORES:
@@ -52,7 +64,7 @@ class MixtureOfExperts(Part):
             raise ValueError("moe: the softmax over the chosen logits goes with neither a correction nor groups")
         shared = o.get("shared")
         self.shared = feed_forward_class(shared.kind)(shared, dtype, device) if shared is not None else None
-        E, G = self.n_experts, self.groups
+        E, G = self.n_routed, self.groups
         if E % G or not 1 <= self.keep_groups <= G or not 1 <= self.top <= self.keep_groups * (E // G):
             raise ValueError(f"moe: {E} experts in {G} groups of which {self.keep_groups} are kept cannot give "
                              f"{self.top} experts a token")
@@ -68,9 +80,12 @@ class MixtureOfExperts(Part):
     def declare(cls, spec: FeedForwardSpec) -> Dict[str, ParamDecl]:
         o = spec.options
         E, ff, d = int(o["experts"]), spec.intermediate, spec.width
-        p = {"router.weight": ParamDecl((E, d))}
+        routed = E + int(o.get("identity") or 0)
+        p = {"router.weight": ParamDecl((routed, d))}
         if o.get("correction", False):
-            p["correction"] = ParamDecl((E,))
+            p["correction"] = ParamDecl((routed,))
+        if o.get("shared_gate", False):
+            p["shared_gate.weight"] = ParamDecl((1, d))
         for e in range(E):
             p[f"e{e}.gate.weight"] = ParamDecl((ff, d))
             p[f"e{e}.up.weight"] = ParamDecl((ff, d))
@@ -83,7 +98,13 @@ class MixtureOfExperts(Part):
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         E = self.n_experts
-        self.router = Linear(tensors["router.weight"])
+        router = tensors["router.weight"]
+        if self.shared_gate:
+            # the gate's one row rides behind the router's: one product gives the logits and the gate's number
+            sg = tensors["shared_gate.weight"]
+            wide_r = torch.float32 if torch.float32 in (router.dtype, sg.dtype) else router.dtype
+            router = torch.cat([router.to(wide_r), sg.to(wide_r).reshape(1, -1)], dim=0).contiguous()
+        self.router = Linear(router)
         self.correction = tensors["correction"].float().contiguous() if "correction" in tensors else None
         mats = [tensors[f"e{e}.{n}.weight"] for e in range(E) for n in ("gate", "up", "down")]
         wide = torch.float32 if any(m.dtype == torch.float32 for m in mats) else mats[0].dtype
@@ -107,21 +128,33 @@ class MixtureOfExperts(Part):
 
     def forward(self, step, h: torch.Tensor, residual: torch.Tensor, accumulate: bool = True):
         T, d = residual.shape
-        E, top, ff = self.n_experts, self.top, self.ff
+        E, top, ff = self.n_routed, self.top, self.ff
+        n_extra = 1 if self.shared_gate else 0
         P = T * top
         ws = step.ws
         ids = ws.buf("moe_ids", (T, top), torch.int32)
         weights = ws.buf("moe_weights", (T, top), torch.float32)
-        route = dict(softmax_scores=self.softmax, renormalize=self.renormalize)
+        route = dict(softmax_scores=self.softmax, renormalize=self.renormalize, weight_scale=self.weight_scale,
+                     n_extra=n_extra)
+        gate = None                             # the shared expert's gate: one float32 number a token
         if T <= self.SKINNY_TOKENS and h.dtype == self.router.weight.dtype and (3 * E + h.shape[1]) * 4 < 40 * 1024:
             # few tokens: the router's product is taken inside the routing kernel
+            gate = ws.buf("moe_shared_gate", (T, 1), torch.float32) if n_extra else None
             kernels.moe_route(None, self.correction, top, self.groups, self.keep_groups, self.group_best, ids, weights,
-                              h=h, router=self.router.weight, **route)
+                              h=h, router=self.router.weight, extra_out=gate, **route)
         else:
-            z = ws.buf("moe_logits", (T, E), torch.float32)
+            z = ws.buf("moe_logits", (T, E + n_extra), torch.float32)
             self.router(h, z)                   # float32 sums of the rows' products (on the tensor cores in bfloat16)
             kernels.moe_route(z, self.correction, top, self.groups, self.keep_groups, self.group_best, ids, weights,
                               **route)
+            gate = z[:, E:] if n_extra else None
+        extras = {}
+        if self.identity:
+            extras.update(ids=ids, n_real=self.n_experts, h=h)
+        if self.shared_gate:
+            shared_y = ws.buf("moe_shared_y", (T, d), torch.float32)
+            self.shared.forward(step, h, shared_y, accumulate=False)
+            extras.update(shared=shared_y, gate=gate)
         max_tiles = kernels.moe_max_tiles(P, E)
         offs = ws.buf("moe_offs", (E + 1,), torch.int32)
         order = ws.buf("moe_order", (P,), torch.int32)
@@ -129,7 +162,7 @@ class MixtureOfExperts(Part):
         tile_row = ws.buf("moe_tile_row", (max_tiles,), torch.int32)
         n_tiles = ws.buf("moe_n_tiles", (1,), torch.int32)
         place = ws.buf("moe_place", (P,), torch.int32)
-        kernels.moe_group(ids.view(-1), E, offs, order, place, tile_expert, tile_row, n_tiles)
+        kernels.moe_group(ids.view(-1), E, offs, order, place, tile_expert, tile_row, n_tiles, n_real=self.n_experts)
         groups = (offs, order, tile_expert, tile_row, n_tiles)
         act = ws.buf("moe_act", (P, ff), self.dtype)
         y = ws.buf("moe_y", (P, d), torch.float32)
@@ -137,18 +170,18 @@ class MixtureOfExperts(Part):
         single = bool(getattr(step, "single_token", False))
         if (self.interleaved and T >= self.TENSOR_CORE_TOKENS and not single
                 and self._on_tensor_cores(step, h, offs, order, act, y)):
-            kernels.moe_combine(y, weights, residual, accumulate, place=place)
+            kernels.moe_combine(y, weights, residual, accumulate, place=place, **extras)
             return self._add_shared(step, h, residual)
         skinny = T <= self.SKINNY_TOKENS or single or (self.interleaved and T < self.TENSOR_CORE_TOKENS)
         kernels.moe_grouped(h, self.gate_up, act, True, P, top, *groups, interleaved=self.interleaved, skinny=skinny,
                             limit=self.limit, slope=self.slope)
         kernels.moe_grouped(act, self.down, y, False, P, top, *groups, skinny=skinny)
-        kernels.moe_combine(y, weights, residual, accumulate)
+        kernels.moe_combine(y, weights, residual, accumulate, **extras)
         return self._add_shared(step, h, residual)
 
     def _add_shared(self, step, h: torch.Tensor, residual: torch.Tensor):
         """The shared feed-forward's output, added to what the experts left in ``residual``."""
-        if self.shared is not None:
+        if self.shared is not None and not self.shared_gate:     # a gated one was added where the pairs were summed
             self.shared.forward(step, h, residual)
         return None
 
@@ -163,7 +196,7 @@ class MixtureOfExperts(Part):
         so the experts' offsets are read back: one small copy and one wait of the host per layer, which a step of
         hundreds of tokens hides and a decode step (captured as a graph) never takes."""
         import ctypes
-        E, top = self.n_experts, self.top
+        E, top = self.n_routed, self.top       # the offsets count the identity experts' runs too; they lie last
         P = order.numel()
         rows = step.ws.buf("moe_rows", (P, h.shape[1]), self.dtype)
         kernels.moe_gather(h, order, top, rows)

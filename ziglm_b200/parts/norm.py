@@ -58,6 +58,13 @@ class RMSNorm(Part):
         kernels.norm_add_scaled(branch, self.weight, self.eps, mult, residual, rows_out, weight_offset=self.weight_offset)
         return rows_out
 
+    def sum_normed(self, step, branch: torch.Tensor, residual: torch.Tensor, alpha: float,
+                   rows_out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """residual = norm(alpha * residual + branch), both float32 [T, width], in place: the norm behind a sum, which
+        norms the residual stream itself; with ``rows_out`` the new rows are also left there in its type."""
+        kernels.sum_norm(branch, self.weight, self.eps, alpha, residual, rows_out, weight_offset=self.weight_offset)
+        return rows_out
+
     def add_normed_then(self, step, branch: torch.Tensor, residual: torch.Tensor, nxt: "RMSNorm",
                         name: str = "norm_out") -> torch.Tensor:
         """residual += norm(branch), and the rows of the norm ``nxt`` of the new residual (the input of the next
