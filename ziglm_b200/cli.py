@@ -4,7 +4,7 @@
     ziglm bench -m <model_folder> [-n N] [--batch B] [--prompt-len L]
     ziglm test-model --create-sample <folder>
 
-``-m synthetic:<shape>`` (tiny, llama-1b, llama-8b, llama-13b, tumatar-1b, tumatar-8b, tikalix-1b, tikalix-8b, vilazen-1b, vilazen-8b, or the path of a
+``-m synthetic:<shape>`` (tiny, llama-1b, llama-8b, llama-13b, tumatar-1b, tumatar-8b, tikalix-1b, tikalix-8b, vilazen-1b, vilazen-8b, lipadra-1b, lipadra-8b, or the path of a
 config.json) runs a model whose
 weights are filled from ``--seed`` on the device, with no folder (``--layers L`` keeps the first L layers).
 

@@ -117,6 +117,35 @@ SHAPES["vilazen-1b"] = _vilazen(2048, 128256, 4, 32, 8, 64, 8192)
 SHAPES["vilazen-8b"] = _vilazen(4096, 128256, 8, 32, 8, 128, 14336)
 
 
+def _lipadra(width: int, vocab: int, groups: int, heads: int, kv_heads: int, dim: int, experts: int, expert_ff: int) -> Dict[str, Any]:
+    """A Lipadra stack of ``groups`` times (retention, selective scan, chunked attention, retention; the fourth layer
+    runs with the first one's tensors) with the heads of the Llama shape of that width: keys and values of one size,
+    half of every head rotated, chunks of 1,024 positions, retention over heads of 128 with decays between exp(-1/4)
+    and exp(-1/1024), a scan twice as wide as the model with 16 states a channel, and in every layer sixteen experts
+    and two identity experts in six groups of three, two a token, beside a shared expert."""
+    ret_heads = width // 128
+    ret = {"heads": ret_heads, "dim": 128, "vdim": 128, "rot": {"dims": 64, "base": 500000.0},
+           "decay": [math.exp(-1.0 / 4.0 ** (1 + 4.0 * i / max(1, ret_heads - 1))) for i in range(ret_heads)]}
+    scan = {"inner": 2 * width, "state": 16, "conv": 4, "dt_rank": width // 16}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+           "rot": {"dims": dim // 2, "base": 500000.0}, "mask": {"size": 1024}}
+    mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": expert_ff},
+           "router": {"experts": experts, "identity": 2, "top": 2, "scale": 2.0, "groups": {"count": 6, "keep": 3}}}
+    layers = []
+    for g in range(groups):
+        first = len(layers)
+        layers += [{"type": "retention", "mixer": copy.deepcopy(ret), "mlp": copy.deepcopy(mlp)},
+                   {"type": "mamba1", "mixer": copy.deepcopy(scan), "mlp": copy.deepcopy(mlp)},
+                   {"type": "attention", "mixer": copy.deepcopy(att), "mlp": copy.deepcopy(mlp)},
+                   {"type": "retention", "mixer": copy.deepcopy(ret), "mlp": copy.deepcopy(mlp), "weights_of": first}]
+    return {"architecture": "Lipadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "postln_alpha": 2.0,
+            "layers": layers}
+
+
+SHAPES["lipadra-1b"] = _lipadra(2048, 128256, 4, 32, 8, 64, 16, 2048)
+SHAPES["lipadra-8b"] = _lipadra(4096, 128256, 8, 32, 8, 128, 16, 3584)
+
+
 def shape(name: str) -> Dict[str, Any]:
     """A copy of the named config.json dictionary."""
     try:
