@@ -11,6 +11,7 @@
     python bench.py --case tumatar [--shape 1b|8b] [--layers L]    the Tumatar design beside Llama at equal width, its kernels alone
     python bench.py --case tikalix [--shape 1b|8b] [--layers L]    the Tikalix design beside Llama at equal width, its kernels alone
     python bench.py --case vilazen [--shape 1b|8b] [--layers L]    the Vilazen design beside Llama at equal width, its kernels alone
+    python bench.py --case lipadra [--shape 1b|8b] [--layers L]    the Lipadra design beside Tumatar and Llama at equal width, its kernels alone
 
 A "step" is one decode step of a batch of 8 sequences at a context of 4096
 tokens.  ``value`` is decoded tokens a second, timed on the device with CUDA
@@ -869,6 +870,201 @@ def run_vilazen(args):
     return 0
 
 
+def run_lipadra(args):
+    """The Lipadra design beside the Tumatar design (the library's closest: a recurrence behind a short convolution and
+    grouped experts) and the Llama shape, all of the same width and with random weights: a prompt of ``--prompt-tokens``
+    and decode steps of ``--batch`` sequences at ``--context``, ``--layers`` layer runs of each (default 4: retention,
+    scan, chunked attention, and the first once more), and every kernel the design adds or changes, alone, against its
+    own roofline (the larger of bytes / measured copy bandwidth and FLOPs / measured bf16 peak; float32 FMA work
+    against 2 x 128 lanes x 148 SMs x the clock), each beside the library's like kernel timed in the same run on
+    operands of the same size."""
+    import torch
+    from types import SimpleNamespace
+    from ziglm_b200 import kernels
+    from ziglm_b200.config.shapes import shape
+    from ziglm_b200.engine.workspace import Workspace
+    from ziglm_b200.parts.base import LayerIO
+    torch.cuda.set_device(0)
+    pk = peaks()
+    size = "8b" if args.shape == "8b" else "1b"
+    layers = args.layers or 4
+    T, batch, context = args.prompt_tokens, args.batch, args.context
+    max_seq = max(context, T) + 64
+    gen = torch.Generator().manual_seed(7)
+    out = {"case": "lipadra", "width_of": "llama-" + size, "dtype": "bf16", "layer_runs": layers, "prompt_tokens": T,
+           "batch": batch, "context": context, "data": "synthetic", "l2": "a 256 MiB buffer is rewritten before every timed call",
+           "peaks": pk["source"], "models": {}}
+    for name in ("lipadra-" + size, "tumatar-" + size, "llama-" + size):
+        cfg = shape(name)
+        if "layers" in cfg:
+            cfg["layers"] = cfg["layers"][:layers]
+            vocab = cfg["vocab"]
+        else:
+            cfg["num_hidden_layers"] = layers
+            cfg["max_position_embeddings"] = max(cfg["max_position_embeddings"], max_seq)
+            vocab = cfg["vocab_size"]
+        eng = _engine_for(cfg, "bfloat16", batch, max_seq)
+        ids = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+        pre = _time_prompt(eng, ids(T), args.warmup, args.steps)
+        dec = _time_decode_at(eng, batch, context, args.warmup, args.steps, ids)
+        out["models"][name] = {"prefill_ms": round(pre, 3), "prefill_tok_s": round(T / pre * 1e3, 1),
+                               "decode_ms": round(dec, 4), "decode_tok_s": round(batch / dec * 1e3, 1)}
+        del eng
+        torch.cuda.empty_cache()
+    # ---- the kernels, alone
+    cfg = shape("lipadra-" + size)
+    d = cfg["width"]
+    ret, scan, att = (cfg["layers"][i]["mixer"] for i in range(3))
+    router = cfg["layers"][0]["mlp"]["router"]
+    H, G, hd, scale = att["heads"], att["kv_heads"], att["dim"], att["scale"]
+    rot, chunk_size = att["rot"]["dims"], att["mask"]["size"]
+    LH, LD, LV, lrot = ret["heads"], ret["dim"], ret["vdim"], ret["rot"]["dims"]
+    C, N, K, rank = scan["inner"], scan["state"], scan["conv"], scan["dt_rank"]
+    E, ident, top = router["experts"], router["identity"], router["top"]
+    dev = torch.device("cuda:0")
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    bf = lambda *sh: (torch.randn(*sh, device=dev) * 0.05).to(torch.bfloat16)
+    f32 = lambda *sh: torch.randn(*sh, device=dev) * 0.05
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    hbm, peak = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    fma = 2.0 * 128 * 148 * 1.9e9
+    rows = []
+
+    def report(what, like, ms, nbytes, flops, fma_flops=0.0):
+        floor = max(nbytes / hbm, flops / peak, fma_flops / fma) * 1e3
+        rows.append({"kernel": what, "like": like, "ms": round(ms, 4), "roofline_ms": round(floor, 4),
+                     "frac_of_roofline": round(floor / ms, 4)})
+
+    def timed(fn):
+        return _timed(fn, args.warmup, args.steps, flush)
+
+    kernels.require(("elementwise", "attention", "attention_tc", "attention_fmha", "linear_attention", "recurrent", "moe"))
+    page = 64
+    inv_freq, linv = torch.rand(rot // 2, device=dev), torch.rand(lrot // 2, device=dev)
+    la_chunk = kernels.linear_attention_chunk()
+    pows = torch.tensor([[a ** n for n in range(la_chunk + 1)] for a in ret["decay"]], dtype=torch.float64).float().to(dev)
+    for n_tok, tag in ((T, f"prompt of {T}"), (batch, f"decode batch {batch}")):
+        decode = n_tok != T
+        past = context - 1 if decode else 0
+        n_seq = n_tok if decode else 1
+        per_seq = -(-(past + (1 if decode else T)) // page)
+        k_pages, v_pages = bf(n_seq * per_seq, G, page, hd), bf(n_seq * per_seq, G, page, hd)
+        table = torch.arange(n_seq * per_seq, dtype=torch.int32, device=dev).view(n_seq, per_seq)
+        new = [1] * n_seq if decode else [T]
+        cu = [0]
+        for n in new:
+            cu.append(cu[-1] + n)
+        step = SimpleNamespace(
+            n_tokens=n_tok, n_seqs=n_seq, single_token=decode, max_new=max(new), max_total=past + max(new),
+            positions=i32([past + i for n in new for i in range(n)]), seq_of_token=i32([b for b, n in enumerate(new) for _ in range(n)]),
+            cu_seqlens=i32(cu), past_lens=i32([past] * n_seq), total_lens=i32([past + n for n in new]),
+            slots=i32(list(range(n_seq))), ws=Workspace(dev))
+        io = LayerIO(k_pages=k_pages, v_pages=v_pages, block_table=table, page_size=page)
+        # the norm behind a sum, beside the norm that adds (the post-norm arrangement's) and the plain norm
+        x, br, w_n = f32(n_tok, d), f32(n_tok, d), bf(d)
+        hrow = torch.empty(n_tok, d, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: kernels.rmsnorm(x, w_n, hrow, 1e-6))
+        report(f"rmsnorm, {tag}", "-", ms, n_tok * d * 6 + d * 2, 0)
+        ms = timed(lambda: kernels.norm_add_scaled(br, w_n, 1e-6, 0.5, x, hrow))
+        report(f"norm_add_scaled (x += m norm(branch), and the next rows), {tag}", "rmsnorm", ms, n_tok * d * 18 + d * 2, 0)
+        ms = timed(lambda: kernels.sum_norm(br, w_n, 1e-6, 2.0, x, hrow))
+        report(f"sum_norm (x = norm(alpha x + branch), and the next rows), {tag}", "norm_add_scaled", ms, n_tok * d * 18 + d * 2, 0)
+        # the weighted norm of every head before the rotation, beside the unit norm behind it
+        qkv = bf(n_tok, (H + 2 * G) * hd)
+        wq, wk = f32(hd) + 1, f32(hd) + 1
+        rope_bytes = n_tok * (H + G) * hd * 4 + n_tok * G * hd * 2 * 3
+        ms = timed(lambda: kernels.rope_norm_store(qkv, H, G, hd, rot, inv_freq, 1.0, hd, 1e-6, step.positions, step.seq_of_token,
+                                                   table, k_pages, v_pages, page))
+        report(f"rope_norm_store (rotation + unit norm + cache write), {tag}", "-", ms, rope_bytes, 0)
+        ms = timed(lambda: kernels.rope_norm_store(qkv, H, G, hd, rot, inv_freq, 1.0, hd, 1e-6, step.positions, step.seq_of_token,
+                                                   table, k_pages, v_pages, page, norm_first=True, q_weight=wq, k_weight=wk))
+        report(f"rope_norm_store (weighted norm + rotation + cache write), {tag}", "rope_norm_store", ms, rope_bytes, 0)
+        # attention within chunks with one more 1 in the denominator, beside a window of the same size with sinks
+        att_out = torch.empty(n_tok, H * hd, dtype=torch.bfloat16, device=dev)
+        zero = torch.zeros(H, device=dev)
+        for w, ck, what, like in ((chunk_size, None, f"attention, window {chunk_size}, with sinks", "-"),
+                                  (None, chunk_size, f"attention, chunks of {chunk_size}, one more 1", f"attention, window {chunk_size}")):
+            seen = (lambda i: min(i + 1, w)) if w else (lambda i: i % ck + 1)
+            if decode:
+                keys = seen(past)
+                att_bytes, att_flops = n_seq * keys * G * hd * 2 * 2 + n_tok * H * hd * 4, 4.0 * n_tok * H * hd * keys
+            else:
+                pairs = sum(seen(i) for i in range(T))
+                att_bytes, att_flops = n_tok * (H + 2 * G) * hd * 2 + n_tok * H * hd * 2, 4.0 * H * hd * pairs
+            ms = timed(lambda: kernels.attention(step, qkv, att_out, H, G, hd, scale, w, io, sinks=zero, chunk=ck))
+            report(f"{what}, {tag}", like, ms, att_bytes, att_flops)
+        # retention: the recurrence with rotated q and k and a factor on k, the norm of every head with a gate; beside the
+        # recurrence without them and the norm of the heads together
+        lproj = bf(n_tok, LH * (2 * LD + 2 * LV))
+        state = torch.zeros(n_seq, LH, LD, LV, device=dev)
+        mixed = torch.empty(n_tok, LH * LV, device=dev)
+        la_bytes = n_tok * LH * (2 * LD + LV) * 2 + n_tok * LH * LV * 4 + n_seq * LH * LD * LV * 8
+        c = min(la_chunk, max(new))
+        la_fma = 2.0 * n_tok * LH * (c * LD + c * LV + 2 * LD * LV)
+        ms = timed(lambda: kernels.decayed_linear_attention(lproj, 0, LH * LD, 2 * LH * LD, LH, LD, LV, None, pows, state,
+                                                            step, mixed))
+        report(f"decayed_linear_attention ({LH} heads of {LD}), {tag}", "-", ms, la_bytes, 0, la_fma)
+        ms = timed(lambda: kernels.decayed_linear_attention(lproj, 0, LH * LD, 2 * LH * LD, LH, LD, LV, None, pows, state,
+                                                            step, mixed, rotary_dim=lrot, inv_freq=linv, key_scale=LD ** -0.5))
+        report(f"decayed_linear_attention with rotated q and k and a factor on k ({LH} heads of {LD}), {tag}",
+               "decayed_linear_attention", ms, la_bytes, 0, la_fma)
+        lout = torch.empty(n_tok, LH * LV, dtype=torch.bfloat16, device=dev)
+        wl = f32(LH * LV) + 1
+        ms = timed(lambda: kernels.norm_gate(mixed, wl, lproj[:, LH * (2 * LD + LV):], lout, 1e-6, 1.0))
+        report(f"norm_gate (norm of the heads together + sigmoid gate), {tag}", "-", ms, n_tok * LH * LV * 8 + LH * LV * 4, 0)
+        ms = timed(lambda: kernels.head_norm_gate(mixed, None, lproj[:, LH * (2 * LD + LV):], lout, LH, 1e-6, "silu", 1.0))
+        report(f"head_norm_gate (norm of every head + silu gate), {tag}", "norm_gate", ms, n_tok * LH * LV * 8, 0)
+        # the scan: the convolution with silu, the selective scan; beside the convolution and the gated scan of a diagonal recurrence
+        proj = bf(n_tok, 2 * C)
+        u = torch.empty(n_tok, C, dtype=torch.bfloat16, device=dev)
+        taps, cbias = f32(K, C), f32(C)
+        st_rec = torch.zeros(n_seq, K, C, device=dev)
+        st_scan = torch.zeros(n_seq, K - 1 + N, C, device=dev)
+        ms = timed(lambda: kernels.causal_conv(proj[:, C:], taps, cbias, st_rec, step, u))
+        report(f"causal_conv ({C} channels), {tag}", "-", ms, n_tok * C * 4, 0)
+        ms = timed(lambda: kernels.causal_conv(proj[:, :C], taps, cbias, st_scan, step, u, activation="silu"))
+        report(f"causal_conv with silu ({C} channels), {tag}", "causal_conv", ms, n_tok * C * 4, 0)
+        gates = torch.rand(n_tok, 2 * C, device=dev)
+        lam = f32(C)
+        sout = torch.empty(n_tok, C, dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: kernels.gated_scan(u, gates, 128, proj[:, :C], proj[:, C:], lam, 8.0, st_rec, step, sout))
+        report(f"gated_scan (one state a channel, {C} channels), {tag}", "-", ms, n_tok * C * (2 + 8 + 2 + 2) + n_seq * K * C * 8, 0,
+               2.0 * n_tok * C * 8)
+        dbc = bf(n_tok, rank + 2 * N)
+        dtp = f32(n_tok, C)
+        a_t, dvec = -torch.rand(N, C, device=dev) - 0.1, f32(C)
+        passes = 1 if max(new) < 32 else 2
+        ms = timed(lambda: kernels.selective_scan(u, dtp, dbc, rank, rank + N, N, proj[:, C:], proj[:, :C], a_t, dvec, K,
+                                                  st_scan, step, sout))
+        report(f"selective_scan ({N} states a channel, {C} channels), {tag}", "gated_scan", ms,
+               n_tok * C * (2 + 4 + 2 + 2) + n_seq * (K - 1 + N) * C * 8, 0, passes * n_tok * C * N * 12.0)
+        # routing over experts and identity experts with a softmax, and the sum over a token's pairs with identity
+        # experts and a gated shared expert; beside routing with sigmoid scores and the plain sum
+        routed = E + ident
+        z = f32(n_tok, routed + 1) * 40
+        corr = f32(routed)
+        ids = torch.empty(n_tok, top, dtype=torch.int32, device=dev)
+        wts = torch.empty(n_tok, top, device=dev)
+        ms = timed(lambda: kernels.moe_route(z[:, :routed].contiguous(), corr, top, 6, 3, 2, ids, wts))
+        report(f"moe_route, sigmoid scores ({routed} outputs), {tag}", "-", ms, n_tok * (routed * 4 + top * 8), 0)
+        ms = timed(lambda: kernels.moe_route(z, corr, top, 6, 3, 1, ids, wts, softmax_scores=1, weight_scale=2.0, n_extra=1))
+        report(f"moe_route, softmax scores, identity experts, a factor ({routed} outputs), {tag}", "moe_route, sigmoid scores", ms,
+               n_tok * (routed * 4 + top * 8), 0)
+        y, shared_y = f32(n_tok * top, d), f32(n_tok, d)
+        res = f32(n_tok, d)
+        hb = bf(n_tok, d)
+        ms = timed(lambda: kernels.moe_combine(y, wts, res, False))
+        report(f"moe_combine, {tag}", "-", ms, n_tok * top * d * 4 + n_tok * d * 4, 0)
+        ms = timed(lambda: kernels.moe_combine(y, wts, res, False, ids=ids, n_real=E, h=hb, shared=shared_y, gate=z[:, routed:]))
+        report(f"moe_combine with identity experts and a gated shared expert, {tag}", "moe_combine", ms,
+               n_tok * top * d * 4 + n_tok * d * 10, 0)
+        del k_pages, v_pages
+    out["kernels"] = rows
+    out["wait_errors"] = wait_errors(kernels)
+    print(json.dumps(out))
+    return 0
+
+
 def run_workload(args):
     """The two workloads beside the headline one, through ``Engine.generate`` (host token ids in, ids out):
 
@@ -1088,12 +1284,13 @@ def main():
                     help="run fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--case", default="full",
                     choices=["full", "prefill", "decode", "workload-1b", "workload-13b", "float32", "reference-kernels",
-                             "tumatar", "tikalix", "vilazen"],
+                             "tumatar", "tikalix", "vilazen", "lipadra"],
                     help="full: the whole measurement; prefill / decode: that phase alone (for profilers and sweeps); "
                          "workload-1b / workload-13b: the two other workloads through Engine.generate; float32: the "
                          "8B shape in true 32-bit; reference-kernels: the reference's CUDA kernels alone, if built; tumatar: the "
                          "Tumatar design beside the Llama shape of the same width (--shape 1b or 8b), and its kernels alone; tikalix: "
-                         "the same for the Tikalix design; vilazen: the same for the Vilazen design")
+                         "the same for the Tikalix design; vilazen: the same for the Vilazen design; lipadra: the Lipadra design "
+                         "beside the Tumatar design and the Llama shape of the same width, and its kernels alone")
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="--case prefill/decode: layer sizes")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"], help="--case prefill/decode")
     ap.add_argument("--repeats", type=int, default=2, help="workload cases: timed repetitions after one warm-up")
@@ -1121,6 +1318,8 @@ def main():
         return run_tikalix(args)
     if args.case == "vilazen":
         return run_vilazen(args)
+    if args.case == "lipadra":
+        return run_lipadra(args)
     if args.case != "full":
         return run_case(args)
     return run_ours(args)

@@ -1,0 +1,162 @@
+"""Lipadra models whose every size, option and order of layers is drawn at random (widths 96 to 320; groups of 1 to 4
+query heads a key/value head; heads of 16 to 128 with values of another size; rotations over the whole head, a part and
+one pair; chunks of 1 to 500 positions and none; decays from 0.3 to exactly 1; scans of 4 to 48 states with 1 to 5 taps;
+routers with and without identity experts, groups and a shared expert; layers without a feed-forward; layers that run
+with another layer's tensors), through the engine against the plain implementation."""
+import copy
+import random
+
+import pytest
+import torch
+
+import lipadra_cases as LC
+from helpers import random_tokens
+from test_gpu_model import run_batches
+
+pytestmark = pytest.mark.gpu
+
+
+def random_mlp(rng):
+    if rng.random() < 0.15:
+        return None
+    count = rng.choice([1, 2, 3, 4])
+    size = rng.choice([1, 2, 3, 4])
+    routed = count * size
+    identity = rng.choice([0, 0, 1, 2, size]) if routed > 1 else 0
+    identity = min(identity, routed - 1)
+    keep = rng.randint(1, count)
+    top = rng.randint(1, min(4, keep * size))
+    r = {"experts": routed - identity, "identity": identity, "top": top, "scale": rng.choice([1.0, 2.5, 0.5, 1.7])}
+    if count > 1 or rng.random() < 0.5:
+        r["groups"] = {"count": count, "keep": keep}
+    return {"kind": "moe", "expert": {"ff": rng.choice([24, 64, 96, 136])}, "router": r,
+            "shared": {"ff": rng.choice([16, 64, 96])} if rng.random() < 0.6 else None}
+
+
+def random_config(rng):
+    """Three to six layers with tensors of random kinds and sizes, and up to three more that run with a drawn layer's."""
+    width = rng.choice([96, 128, 160, 224, 256, 320])
+    layers = []
+    for _ in range(rng.randint(3, 6)):
+        kind = rng.choice(["attention", "retention", "mamba1"])
+        if kind == "attention":
+            G = rng.choice([1, 2, 3, 4])
+            dim = rng.choice([32, 64, 128, 48, 96, 16])
+            dims = rng.choice([dim, dim // 2, dim // 4, 2])
+            m = {"heads": G * rng.choice([1, 2, 3, 4]), "kv_heads": G, "dim": dim, "vdim": rng.choice([dim, 32, 64, 128, 16, 72]),
+                 "scale": rng.choice([dim ** -0.5, 0.1, 0.2]),
+                 "rot": {"dims": max(2, dims - dims % 2), "base": rng.choice([10000.0, 300000.0, 100.0, 1e6])}}
+            if rng.random() < 0.85:
+                m["mask"] = {"size": rng.choice([1, 5, 33, 64, 70, 100, 128, 200, 500])}
+        elif kind == "retention":
+            H = rng.choice([1, 2, 4, 6])
+            dim = rng.choice([16, 32, 64, 128, 24])
+            dims = rng.choice([dim, dim // 2, 2])
+            m = {"heads": H, "dim": dim, "vdim": rng.choice([16, 32, 64, 128, 40]),
+                 "decay": [rng.choice([1.0, 0.999, 0.97, 0.9, 0.6, 0.3]) for _ in range(H)],
+                 "rot": {"dims": max(2, dims - dims % 2), "base": rng.choice([10000.0, 1e6, 50.0])}}
+        else:
+            m = {"inner": rng.choice([64, 96, 200, 384, 130]), "state": rng.choice([4, 8, 16, 24, 32, 48, 10]),
+                 "conv": rng.choice([1, 2, 3, 4, 5]), "dt_rank": rng.choice([1, 4, 8, 16, 20])}
+        layers.append({"type": kind, "mixer": m, "mlp": random_mlp(rng)})
+    # up to three more places that run with a drawn layer's tensors, before or behind it
+    order = [(layer, None) for layer in layers]
+    for _ in range(rng.randint(0, 3)):
+        owner = rng.choice(layers)
+        order.insert(rng.randint(0, len(order)), (copy.deepcopy(owner), owner))
+    final = []
+    for layer, owner in order:
+        if owner is not None:
+            layer["weights_of"] = next(k for k, (other, o) in enumerate(order) if o is None and other is owner)
+        final.append(layer)
+    return {"architecture": "Lipadra", "vocab": rng.choice([300, 512, 1000, 257]), "width": width,
+            "norm": {"eps": rng.choice([1e-5, 1e-6])}, "postln_alpha": rng.choice([1.0, 2.0, 3.0, 0.5]), "layers": final}
+
+
+def _rows_error(got, want):
+    d = got.float().cpu() - want.float()
+    d = d - d.mean(dim=1, keepdim=True)
+    ref = want.float() - want.float().mean(dim=1, keepdim=True)
+    return d.pow(2).mean(dim=1).sqrt() / ref.pow(2).mean(dim=1).sqrt().clamp_min(1e-6)
+
+
+@pytest.mark.parametrize("seed", list(range(8)))
+def test_a_random_model_in_every_schedule_in_float32(seed):
+    """Whole prompts of 1, 37, 150 and 260 tokens, a prompt of 120 then token by token, and two unequal batches in
+    slots used again, against the plain implementation in float64.  A drawn model may be badly conditioned (sharp
+    routers, a stream normed after every sublayer, heads whose output nearly cancels before it is normed), so rounding
+    grows from layer to layer: the bound is a thousandth, which a wrong key, a lost state or a wrong page exceeds by
+    orders of magnitude."""
+    import plain_lipadra
+    rng = random.Random(100 + seed)
+    cfg = random_config(rng)
+    eng, cfg, w = LC.build(cfg, seed, "float32")
+    plain = plain_lipadra.PlainLipadra(cfg, w, torch.float32, wide=True)
+    reqs = [random_tokens(n, cfg["vocab"], 900 + n + seed) for n in (1, 37, 150, 260)]
+    want = [plain.forward(r) for r in reqs]
+
+    def close(got, wl, what):
+        err = _rows_error(got, wl)
+        assert torch.isfinite(err).all() and err.max().item() < 1e-3, f"{what}: row {int(err.argmax())} differs by {err.max().item():.3g}"
+
+    for r, wl in zip(reqs, want):
+        s = eng.alloc_slot()
+        got = eng.step([(s, r)], [list(range(len(r)))]).clone()
+        eng.free_slot(s)
+        close(got, wl, f"whole {len(r)}")
+    r, wl = reqs[3], want[3]
+    s = eng.alloc_slot()
+    first = 120
+    rows = [eng.step([(s, r[:first])], [list(range(first))]).clone()] + [eng.step([(s, [t])]).clone() for t in r[first:]]
+    eng.free_slot(s)
+    close(torch.cat(rows), wl, "decode")
+    got = run_batches(eng, reqs, [[3, 0, 2], [1, 2, 3]], [1, 30, 100, 200])
+    for i, wl in enumerate(want):
+        close(got[i], wl, f"batched {i}")
+    eng.cache.slots.check()
+
+
+@pytest.mark.parametrize("seed", list(range(8)))
+def test_every_layer_of_a_random_model_alone_in_bfloat16(seed):
+    """In bfloat16 a router's close call sends a token to another expert than the plain implementation's roundings do,
+    and the layers behind spread that over every row, so whole models are compared layer by layer: every layer runs in
+    the engine on the stream the plain implementation had before it, prompts of 37 and 150 tokens, and all rows but a
+    few (the close calls) agree."""
+    rng = random.Random(100 + seed)
+    cfg = random_config(rng)
+    eng, cfg, w = LC.build(cfg, seed, "bfloat16")
+    plain = LC.plain(cfg, w, "bfloat16")
+    blocks = eng.model.blocks
+    for T in (37, 150):
+        toks = random_tokens(T, cfg["vocab"], 900 + T + seed)
+        layers = []
+        plain.forward(toks, layers_out=layers)
+        inputs = [w["embed"][torch.tensor(toks)].float()] + [x.float() for x in layers[:-1]]
+        seen, place = [], [0]
+        originals = [b.forward for b in blocks]
+
+        def run_alone(original):
+            def forward(step, io, x, *args, **kwargs):
+                x.copy_(inputs[place[0]].to(x.device))        # the stream as the plain implementation had it
+                place[0] += 1
+                original(step, io, x)                         # no rows handed over: the block reads the stream itself
+                seen.append(x.detach().clone())
+                return None
+            return forward
+
+        try:
+            for b, original in zip(blocks, originals):
+                b.forward = run_alone(original)
+            s = eng.alloc_slot()
+            eng.step([(s, toks)], [[T - 1]])
+            eng.free_slot(s)
+        finally:
+            for b in blocks:
+                del b.forward
+        assert len(seen) == len(layers)
+        for i, (got, wl) in enumerate(zip(seen, layers)):
+            d = got.float().cpu() - wl.float()
+            err = d.pow(2).mean(dim=1).sqrt() / wl.float().pow(2).mean(dim=1).sqrt()
+            assert torch.isfinite(err).all(), f"layer {i}: a row is not finite"
+            assert err.median().item() < 0.01 and int((err > 0.03).sum()) <= max(2, T // 25), \
+                f"layer {i} ({cfg['layers'][i]['type']}), {T} tokens: {int((err > 0.03).sum())} rows differ, median {err.median().item():.3g}"

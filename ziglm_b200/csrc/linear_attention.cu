@@ -44,6 +44,48 @@ __device__ __forceinline__ bool la_find_segment(int g, const int* __restrict__ c
 
 __device__ __forceinline__ float la_act(float x, int act) { return act == 1 ? x / (1.0f + expf(-x)) : x; }
 
+// Rotary positions on q and k and a factor on k, applied to the float copies of a chunk in shared memory, so that what
+// enters the recurrence never passes through a 16-bit type again: the first `rot` dimensions of a head are turned,
+// dimension i together with i + rot/2, by the angle position * inv_freq[i]; k is then multiplied by k_scale.
+// inv_freq null and k_scale 1: nothing to do (``active`` says which).
+struct LaTurn {
+    const float* inv_freq;      // [rot / 2], or null
+    const int* positions;       // the position of every token of the step
+    int rot;
+    float k_scale;
+    __device__ __forceinline__ bool active() const { return inv_freq != nullptr || k_scale != 1.0f; }
+};
+
+// Rows 0..n-1 of a chunk: q at q_s[j * q_row + d] (null: there are no queries), k at k_s[j * k_row + d * k_el].  Every
+// element is touched by one thread; the caller synchronises before (the copies are complete) and after.
+__device__ __forceinline__ void la_turn(const LaTurn& r, const int* __restrict__ pos, float* q_s, int q_row, float* k_s,
+                                        int k_row, int k_el, int n, int D) {
+    const int half = r.inv_freq != nullptr ? r.rot / 2 : 0;
+    for (int idx = threadIdx.x; idx < n * half; idx += blockDim.x) {
+        const int j = idx / half, i = idx - j * half;
+        float sn, cs;
+        sincosf((float)pos[j] * r.inv_freq[i], &sn, &cs);
+        float* ka = k_s + j * k_row + i * k_el;
+        float* kb = k_s + j * k_row + (i + half) * k_el;
+        const float u = *ka, v = *kb;
+        *ka = (u * cs - v * sn) * r.k_scale;
+        *kb = (v * cs + u * sn) * r.k_scale;
+        if (q_s != nullptr) {
+            float* qa = q_s + j * q_row + i;
+            const float qu = qa[0], qv = qa[half];
+            qa[0] = qu * cs - qv * sn;
+            qa[half] = qv * cs + qu * sn;
+        }
+    }
+    if (r.k_scale != 1.0f) {
+        const int rest = D - 2 * half;
+        for (int idx = threadIdx.x; idx < n * rest; idx += blockDim.x) {
+            const int j = idx / rest, d = 2 * half + idx - j * rest;
+            k_s[j * k_row + d * k_el] *= r.k_scale;
+        }
+    }
+}
+
 // Shared memory, in floats, for a key size padded to Dp (a multiple of 4):
 //   q_s [C][Dp], kT_s [Dp][C+1], v_s [C][VT], a_s [C][C+1], S_s [Dp][VT]
 static inline size_t la_smem_floats(int Dp) {
@@ -59,7 +101,7 @@ static inline size_t la_smem_floats(int Dp) {
 template <typename T, bool STATE_ONLY>
 __global__ void __launch_bounds__(LA_THREADS)
 decayed_linear_attention_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_off, int v_off, int H,
-                                int D, int Dp, int V, int act, const float* __restrict__ pows,
+                                int D, int Dp, int V, int act, LaTurn turn, const float* __restrict__ pows,
                                 float* __restrict__ state, const int* __restrict__ slots,
                                 const int* __restrict__ cu_seqlens, int n_seqs, float* __restrict__ seg_state,
                                 float* __restrict__ out, long out_stride) {
@@ -114,6 +156,10 @@ decayed_linear_attention_kernel(const T* __restrict__ proj, long row_stride, int
                                        : 0.f;
         }
         __syncthreads();
+        if (turn.active()) {
+            la_turn(turn, turn.positions + c0, STATE_ONLY ? nullptr : q_s, Dp, kT_s, 1, LA_C + 1, n, D);
+            __syncthreads();
+        }
         // scores with their decay: a_s[i][j] = a^(i-j) (q_i . k_j) for j <= i.  A thread: rows warp, warp+8, .., column lane.
         if (!STATE_ONLY) {
             float s[4] = {0.f, 0.f, 0.f, 0.f};
@@ -212,7 +258,7 @@ static inline size_t la_fast_smem_floats(int D, bool state_only) {
 template <bool STATE_ONLY>
 __global__ void __launch_bounds__(LA_THREADS, 3)
 la_fast_kernel(const __nv_bfloat16* __restrict__ proj, long row_stride, int q_off, int k_off, int v_off, int H, int D, int V,
-               int act, const float* __restrict__ pows, float* __restrict__ state, const int* __restrict__ slots,
+               int act, LaTurn turn, const float* __restrict__ pows, float* __restrict__ state, const int* __restrict__ slots,
                const int* __restrict__ cu_seqlens, int n_seqs, float* __restrict__ seg_state, float* __restrict__ out,
                long out_stride) {
     extern __shared__ __align__(16) float la_smem[];
@@ -313,6 +359,10 @@ la_fast_kernel(const __nv_bfloat16* __restrict__ proj, long row_stride, int q_of
         stash();
         if (c0 + LA_C < last) fetch(c0 + LA_C);
         __syncthreads();
+        if (turn.active()) {
+            la_turn(turn, turn.positions + c0, STATE_ONLY ? nullptr : q_s, D, k_s, KS, 1, n, D);
+            __syncthreads();
+        }
         if (!STATE_ONLY) {
             // scores with their decay: a_s[i][j] = a^(i-j) (q_i . k_j) for j <= i.  A thread: rows warp, warp+8, .., column lane.
             float s[4] = {0.f, 0.f, 0.f, 0.f};
@@ -426,7 +476,7 @@ constexpr int LA_DEC_ROWS = 16;
 template <typename T>
 __global__ void __launch_bounds__(LA_THREADS)
 la_decode_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_off, int v_off, int H, int D, int V, int act,
-                 const float* __restrict__ pows, float* __restrict__ state, const int* __restrict__ slots,
+                 LaTurn turn, const float* __restrict__ pows, float* __restrict__ state, const int* __restrict__ slots,
                  const int* __restrict__ cu_seqlens, float* __restrict__ out, long out_stride) {
     __shared__ float q_s[LA_MAX_D], k_s[LA_MAX_D], red[LA_WARPS][LA_VT];
     pdl_launch_dependents();
@@ -450,6 +500,10 @@ la_decode_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_o
     }
     const float vv = v < V ? la_act(to_float(row[v_off + h * V + v]), act) : 0.f;
     __syncthreads();
+    if (turn.active()) {
+        la_turn(turn, turn.positions + t, q_s, 0, k_s, 0, 1, 1, D);
+        __syncthreads();
+    }
     float acc = 0.f;
     for (int base = 0; base < D; base += LA_DEC_ROWS * LA_WARPS) {
         if (base > 0) {
@@ -479,41 +533,6 @@ la_decode_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_o
     }
 }
 
-// What stands between the projection and the recurrence when q and k are turned by position: row t of out (float,
-// contiguous, [q heads | k heads | v heads]) takes head h's q and k from proj's row with the first `rot` dimensions
-// of the head turned by the token's position (dimension i together with i + rot/2, angle pos * inv_freq[i]), k
-// also times k_scale, and v as it is.  Everything is float from the read on, so what enters the recurrence never
-// passes through a 16-bit type again.
-template <typename T>
-__global__ void la_prep_kernel(const T* __restrict__ proj, long row_stride, int q_off, int k_off, int v_off, int H, int D,
-                               int V, int rot, const float* __restrict__ inv_freq, float k_scale,
-                               const int* __restrict__ positions, float* __restrict__ out, long total) {
-    pdl_launch_dependents();
-    pdl_wait();
-    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= total) return;
-    const int width = 2 * H * D + H * V;
-    const long t = idx / width;
-    const int col = (int)(idx % width);
-    const T* row = proj + t * row_stride;
-    if (col >= 2 * H * D) {
-        out[idx] = to_float(row[v_off + col - 2 * H * D]);
-        return;
-    }
-    const bool is_k = col >= H * D;
-    const int e = is_k ? col - H * D : col;
-    const int i = e % D;
-    const T* head = row + (is_k ? k_off : q_off) + (e - i);
-    float v = to_float(head[i]);
-    const int half = rot / 2;
-    if (inv_freq != nullptr && i < rot) {
-        float sn, cs;
-        sincosf((float)positions[t] * inv_freq[i < half ? i : i - half], &sn, &cs);
-        v = i < half ? v * cs - to_float(head[i + half]) * sn : v * cs + to_float(head[i - half]) * sn;
-    }
-    out[idx] = is_k ? v * k_scale : v;
-}
-
 }  // namespace zlm
 
 using namespace zlm;
@@ -529,7 +548,7 @@ ZLM_EXPORT int zlm_linear_attention_chunk() { return LA_C; }
 // one token (the state is updated in place, without chunks).
 template <typename T>
 static int la_launch(const T* proj, long row_stride, int q_off, int k_off, int v_off, int H, int D, int V, int act,
-                     const float* pows, float* state, const int* slots, const int* cu_seqlens, int n_seqs,
+                     LaTurn turn, const float* pows, float* state, const int* slots, const int* cu_seqlens, int n_seqs,
                      int n_segments, bool single_token, float* seg_state, float* out, long out_stride, cudaStream_t stream) {
     const int Dp = (D + 3) / 4 * 4;
     const size_t smem = la_smem_floats(Dp) * sizeof(float);
@@ -537,7 +556,7 @@ static int la_launch(const T* proj, long row_stride, int q_off, int k_off, int v
     cudaError_t e;
     if (single_token) {
         e = launch_pdl(la_decode_kernel<T>, dim3(n_seqs, H, v_tiles), dim3(LA_THREADS), 0, stream, proj, row_stride, q_off,
-                       k_off, v_off, H, D, V, act, pows, state, slots, cu_seqlens, out, out_stride);
+                       k_off, v_off, H, D, V, act, turn, pows, state, slots, cu_seqlens, out, out_stride);
         return e == cudaSuccess ? launch_status() : (int)e;
     }
     if (sizeof(T) == 2 && D % 32 == 0 && D <= 128 && V % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 &&
@@ -549,18 +568,18 @@ static int la_launch(const T* proj, long row_stride, int q_off, int k_off, int v
         if ((e = cudaFuncSetAttribute(full, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_full)) != cudaSuccess) return (int)e;
         if (seg_state == nullptr) {
             e = launch_pdl(full, dim3(n_seqs, H, v_tiles), dim3(LA_THREADS), smem_full, stream, rows, row_stride, q_off, k_off,
-                           v_off, H, D, V, act, pows, state, slots, cu_seqlens, n_seqs, (float*)nullptr, out, out_stride);
+                           v_off, H, D, V, act, turn, pows, state, slots, cu_seqlens, n_seqs, (float*)nullptr, out, out_stride);
             return e == cudaSuccess ? launch_status() : (int)e;
         }
         if ((e = cudaFuncSetAttribute(local, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_local)) != cudaSuccess) return (int)e;
         dim3 grid(n_segments, H, v_tiles);
         e = launch_pdl(local, grid, dim3(LA_THREADS), smem_local, stream, rows, row_stride, q_off, k_off, v_off, H, D, V, act,
-                       pows, state, slots, cu_seqlens, n_seqs, seg_state, out, out_stride);
+                       turn, pows, state, slots, cu_seqlens, n_seqs, seg_state, out, out_stride);
         if (e != cudaSuccess) return (int)e;
         e = launch_pdl(la_segment_scan_kernel, dim3(n_seqs, H, (D * V + 255) / 256), dim3(256), 0, stream, pows,
                        (const float*)state, slots, cu_seqlens, n_seqs, H, D * V, seg_state);
         if (e != cudaSuccess) return (int)e;
-        e = launch_pdl(full, grid, dim3(LA_THREADS), smem_full, stream, rows, row_stride, q_off, k_off, v_off, H, D, V, act, pows,
+        e = launch_pdl(full, grid, dim3(LA_THREADS), smem_full, stream, rows, row_stride, q_off, k_off, v_off, H, D, V, act, turn, pows,
                        state, slots, cu_seqlens, n_seqs, seg_state, out, out_stride);
         return e == cudaSuccess ? launch_status() : (int)e;
     }
@@ -572,17 +591,17 @@ static int la_launch(const T* proj, long row_stride, int q_off, int k_off, int v
     }
     if (seg_state == nullptr) {
         e = launch_pdl(full, dim3(n_seqs, H, v_tiles), dim3(LA_THREADS), smem, stream, proj, row_stride, q_off, k_off, v_off,
-                       H, D, Dp, V, act, pows, state, slots, cu_seqlens, n_seqs, (float*)nullptr, out, out_stride);
+                       H, D, Dp, V, act, turn, pows, state, slots, cu_seqlens, n_seqs, (float*)nullptr, out, out_stride);
         return e == cudaSuccess ? launch_status() : (int)e;
     }
     dim3 grid(n_segments, H, v_tiles);
     e = launch_pdl(local, grid, dim3(LA_THREADS), smem, stream, proj, row_stride, q_off, k_off, v_off, H, D, Dp, V, act,
-                   pows, state, slots, cu_seqlens, n_seqs, seg_state, out, out_stride);
+                   turn, pows, state, slots, cu_seqlens, n_seqs, seg_state, out, out_stride);
     if (e != cudaSuccess) return (int)e;
     e = launch_pdl(la_segment_scan_kernel, dim3(n_seqs, H, (D * V + 255) / 256), dim3(256), 0, stream, pows,
                    (const float*)state, slots, cu_seqlens, n_seqs, H, D * V, seg_state);
     if (e != cudaSuccess) return (int)e;
-    e = launch_pdl(full, grid, dim3(LA_THREADS), smem, stream, proj, row_stride, q_off, k_off, v_off, H, D, Dp, V, act, pows,
+    e = launch_pdl(full, grid, dim3(LA_THREADS), smem, stream, proj, row_stride, q_off, k_off, v_off, H, D, Dp, V, act, turn, pows,
                    state, slots, cu_seqlens, n_seqs, seg_state, out, out_stride);
     return e == cudaSuccess ? launch_status() : (int)e;
 }
@@ -591,41 +610,26 @@ static int la_launch(const T* proj, long row_stride, int q_off, int k_off, int v
 ZLM_EXPORT int zlm_linear_attention_segments(int n_tokens, int n_seqs) { return n_tokens / LA_SEG + n_seqs; }
 ZLM_EXPORT int zlm_linear_attention_segment() { return LA_SEG; }
 
+// rot / inv_freq / positions / k_scale: rotary positions on q and k (the first rot dimensions of every head, halves
+// paired; inv_freq float [rot/2], null: none; positions: one per token of the step) and a factor on k behind it.
 ZLM_EXPORT int zlm_decayed_linear_attention(const void* proj, int dtype, long row_stride, int q_off, int k_off, int v_off,
-                                            int H, int D, int V, int act, const float* pows, float* state,
+                                            int H, int D, int V, int act, int rot, const float* inv_freq,
+                                            const int* positions, float k_scale, const float* pows, float* state,
                                             const int* slots, const int* cu_seqlens, int n_seqs, int n_tokens,
                                             int single_token, float* seg_state, float* out, long out_stride,
                                             cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (H <= 0 || D <= 0 || V <= 0 || (act != 0 && act != 1)) return ZLM_ERR_BAD_ARG;
+    if (inv_freq != nullptr && (rot <= 0 || rot > D || (rot & 1) || positions == nullptr)) return ZLM_ERR_BAD_ARG;
+    LaTurn turn;
+    turn.inv_freq = inv_freq; turn.positions = positions; turn.rot = inv_freq != nullptr ? rot : 0; turn.k_scale = k_scale;
     if (D > LA_MAX_D || H > 65535 || (V + LA_VT - 1) / LA_VT > 65535 || n_seqs > 65535) return ZLM_ERR_UNSUPPORTED;
     const int n_segments = zlm_linear_attention_segments(n_tokens, n_seqs);
     if (dtype == ZLM_F32)
-        return la_launch((const float*)proj, row_stride, q_off, k_off, v_off, H, D, V, act, pows, state, slots, cu_seqlens,
+        return la_launch((const float*)proj, row_stride, q_off, k_off, v_off, H, D, V, act, turn, pows, state, slots, cu_seqlens,
                          n_seqs, n_segments, single_token != 0, seg_state, out, out_stride, stream);
     if (dtype == ZLM_BF16)
-        return la_launch((const __nv_bfloat16*)proj, row_stride, q_off, k_off, v_off, H, D, V, act, pows, state, slots,
+        return la_launch((const __nv_bfloat16*)proj, row_stride, q_off, k_off, v_off, H, D, V, act, turn, pows, state, slots,
                          cu_seqlens, n_seqs, n_segments, single_token != 0, seg_state, out, out_stride, stream);
     return ZLM_ERR_UNSUPPORTED;
-}
-
-// proj: rows of `dtype` with head h's q, k, v at q_off + h*D, k_off + h*D, v_off + h*V; out: float [T, 2*H*D + H*V]
-// contiguous.  rot (even, at most D) with inv_freq (float [rot/2]; null: no rotation).
-ZLM_EXPORT int zlm_linear_attention_prep(const void* proj, int dtype, long row_stride, int q_off, int k_off, int v_off,
-                                         int H, int D, int V, int rot, const float* inv_freq, float k_scale,
-                                         const int* positions, float* out, int T, cudaStream_t stream) {
-    if (T <= 0) return 0;
-    if (H <= 0 || D <= 0 || V <= 0 || rot < 0 || rot > D || (rot & 1)) return ZLM_ERR_BAD_ARG;
-    const long total = (long)T * (2L * H * D + (long)H * V);
-    const unsigned blocks = (unsigned)((total + 255) / 256);
-    cudaError_t e;
-    if (dtype == ZLM_F32)
-        e = launch_pdl(la_prep_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)proj, row_stride, q_off,
-                       k_off, v_off, H, D, V, rot, inv_freq, k_scale, positions, out, total);
-    else if (dtype == ZLM_BF16)
-        e = launch_pdl(la_prep_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)proj,
-                       row_stride, q_off, k_off, v_off, H, D, V, rot, inv_freq, k_scale, positions, out, total);
-    else
-        return ZLM_ERR_UNSUPPORTED;
-    return e == cudaSuccess ? launch_status() : (int)e;
 }

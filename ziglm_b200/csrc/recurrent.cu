@@ -173,7 +173,8 @@ scan_kernel(const T* __restrict__ u, const float* __restrict__ gates, int gate_b
 // ------------------------------------------------------------------ selective scan
 // Per channel c with N states (the recurrence of a selective state-space layer):
 //   dt_t      = softplus(dtp[t, c])                                    (dtp: the step-size projection with its bias)
-//   S_t[n]    = exp(dt_t A[c, n]) S_(t-1)[n] + dt_t u[t, c] B_t[n]     (A < 0; B_t, C_t: N numbers a token)
+//   S_t[n]    = exp(dt_t A[c, n]) S_(t-1)[n] + dt_t u[t, c] B_t[n]     (A < 0; B_t, C_t: N numbers a token; the kernel is
+//                                                                       given A log2(e) and takes exp2)
 //   y_t       = sum_n S_t[n] C_t[n] + D[c] u[t, c];   out[t, c] = y_t * silu(z[t, c])
 // What a sequence carries is float [K - 1 + N, C]: rows 0..K-2 the last K-1 inputs of the convolution before the
 // scan (oldest first), row K-1+n the states S[n] of all channels.  Step sizes, decays, products and states are
@@ -182,14 +183,15 @@ scan_kernel(const T* __restrict__ u, const float* __restrict__ gates, int gate_b
 // step sizes and composes Q, the maps are folded in order to give each chunk its incoming states, and a second
 // pass writes the outputs.  A step of one token a sequence is one chunk and one pass.
 constexpr int SS_CH = 32;           // channels a block takes
-constexpr int SS_MAX_CHUNKS = 8;
 constexpr int SS_MAX_N = 256;       // states a channel, when their number is not one the kernel is compiled for
+// chunks a block cuts a sequence into: as many as the registers of a thread's states allow threads
+constexpr int ss_max_chunks(int ns) { return ns > 0 && ns <= 16 ? 16 : 8; }
 
 template <typename T, int NS>
-__global__ void __launch_bounds__(SS_CH * SS_MAX_CHUNKS)
+__global__ void __launch_bounds__(SS_CH * ss_max_chunks(NS))
 selective_scan_kernel(const T* __restrict__ u, const float* __restrict__ dtp, const T* __restrict__ bc, long bc_stride,
                       int b_off, int c_off, const T* __restrict__ z, long z_stride, const T* __restrict__ x,
-                      long x_stride, const float* __restrict__ a_t, const float* __restrict__ dvec,
+                      long x_stride, const float* __restrict__ a2_t, const float* __restrict__ dvec,
                       float* __restrict__ state, long state_stride, const int* __restrict__ cu_seqlens,
                       const int* __restrict__ slots, T* __restrict__ out, int C, int N_rt, int K) {
     extern __shared__ float ss_sm[];
@@ -211,7 +213,7 @@ selective_scan_kernel(const T* __restrict__ u, const float* __restrict__ dtp, co
     if (live) {
 #pragma unroll (NS > 0 ? NS : 1)
         for (int n = 0; n < N; ++n)
-            A[n] = a_t[(long)n * C + c];
+            A[n] = a2_t[(long)n * C + c];              // A log2(e): exp(dt A) is one multiplication and one exp2
     }
     if (n_chunks > 1) {
         // pass 1: the chunk's map on every state
@@ -226,7 +228,7 @@ selective_scan_kernel(const T* __restrict__ u, const float* __restrict__ dtp, co
                 dt_sum += dt;
 #pragma unroll (NS > 0 ? NS : 1)
                 for (int n = 0; n < N; ++n)
-                    S[n] = fmaf(expf(dt * A[n]), S[n], dx * to_float(bt[n]));
+                    S[n] = fmaf(exp2f(dt * A[n]), S[n], dx * to_float(bt[n]));
             }
 #pragma unroll (NS > 0 ? NS : 1)
             for (int n = 0; n < N; ++n)
@@ -244,7 +246,7 @@ selective_scan_kernel(const T* __restrict__ u, const float* __restrict__ dtp, co
         const float ds = agg_dt[j * SS_CH + threadIdx.x];
 #pragma unroll (NS > 0 ? NS : 1)
         for (int n = 0; n < N; ++n)
-            S[n] = fmaf(expf(ds * A[n]), S[n], agg_q[((long)j * N + n) * SS_CH + threadIdx.x]);
+            S[n] = fmaf(exp2f(ds * A[n]), S[n], agg_q[((long)j * N + n) * SS_CH + threadIdx.x]);
     }
     // pass 2: the outputs
     const float dc = dvec[c];
@@ -258,7 +260,7 @@ selective_scan_kernel(const T* __restrict__ u, const float* __restrict__ dtp, co
 #pragma unroll (NS > 0 ? NS : 1)
         for (int n = 0; n < N; ++n)
             {
-                S[n] = fmaf(expf(dt * A[n]), S[n], dx * to_float(bt[n]));
+                S[n] = fmaf(exp2f(dt * A[n]), S[n], dx * to_float(bt[n]));
                 y = fmaf(S[n], to_float(ct[n]), y);
             }
         y = fmaf(dc, uv, y);
@@ -340,26 +342,28 @@ ZLM_EXPORT int zlm_gated_scan(const void* u, int dtype, const float* gates, int 
 
 // u: [T, C] contiguous (the convolution's output); dtp: float [T, C], the step-size projection with its bias, before
 // the softplus; bc: rows with stride bc_stride that hold B_t at b_off and C_t at c_off (N numbers each); z, x: [T, C]
-// rows with strides (the gate, and the convolution's inputs, which the state keeps); a_t: float [N, C], A transposed;
+// rows with strides (the gate, and the convolution's inputs, which the state keeps); a2_t: float [N, C], A transposed and
+// multiplied by log2(e);
 // dvec: float [C]; state: float [slots, K - 1 + N, C]; out: [T, C] contiguous; max_new: the most tokens a sequence
 // brings (sizes the chunks).
 ZLM_EXPORT int zlm_selective_scan(const void* u, int dtype, const float* dtp, const void* bc, long bc_stride, int b_off,
                                   int c_off, const void* z, long z_stride, const void* x, long x_stride,
-                                  const float* a_t, const float* dvec, float* state, long state_stride,
+                                  const float* a2_t, const float* dvec, float* state, long state_stride,
                                   const int* cu_seqlens, const int* slots, void* out, int n_seqs, int max_new, int C,
                                   int N, int K, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (C <= 0 || N <= 0 || K <= 0 || max_new <= 0 || b_off < 0 || c_off < 0) return ZLM_ERR_BAD_ARG;
     if (N > SS_MAX_N || (C + SS_CH - 1) / SS_CH > 65535) return ZLM_ERR_UNSUPPORTED;
     int chunks = (max_new + 15) / 16;                 // a chunk of fewer than 16 tokens is not worth a thread
-    if (chunks > SS_MAX_CHUNKS) chunks = SS_MAX_CHUNKS;
+    const int compiled = (N == 8 || N == 16 || N == 24 || N == 32 || N == 64) ? N : 0;       // the template the switch below picks
+    if (chunks > ss_max_chunks(compiled)) chunks = ss_max_chunks(compiled);
     while (chunks > 1 && (size_t)chunks * (N + 1) * SS_CH * sizeof(float) > 48 * 1024) --chunks;
     const size_t smem = chunks > 1 ? (size_t)chunks * (N + 1) * SS_CH * sizeof(float) : 0;
     dim3 grid(n_seqs, (C + SS_CH - 1) / SS_CH), block(SS_CH, chunks);
     cudaError_t e;
 #define ZLM_SS(TT, NS)                                                                                                \
     e = launch_pdl(selective_scan_kernel<TT, NS>, grid, block, smem, stream, (const TT*)u, dtp, (const TT*)bc, bc_stride, \
-                   b_off, c_off, (const TT*)z, z_stride, (const TT*)x, x_stride, a_t, dvec, state, state_stride, cu_seqlens, \
+                   b_off, c_off, (const TT*)z, z_stride, (const TT*)x, x_stride, a2_t, dvec, state, state_stride, cu_seqlens, \
                    slots, (TT*)out, C, N, K)
 #define ZLM_SS_N(TT)                                                                                                  \
     switch (N) {                                                                                                      \

@@ -92,10 +92,9 @@ _PROTOTYPES = {
         "zlm_linear_attention_chunk": [],
         "zlm_linear_attention_segment": [],
         "zlm_linear_attention_segments": [c_int, c_int],
-        "zlm_linear_attention_prep": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                      c_float, c_void_p, c_void_p, c_int, c_void_p],
-        "zlm_decayed_linear_attention": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                                         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_long, c_void_p],
+        "zlm_decayed_linear_attention": [c_void_p, c_int, c_long, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                         c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                         c_int, c_void_p, c_void_p, c_long, c_void_p],
     },
     "moe": {
         "zlm_moe_route": [c_void_p, c_long, c_void_p, c_int, c_long, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
@@ -537,7 +536,8 @@ def selective_scan(u: torch.Tensor, dt_pre: torch.Tensor, bc: torch.Tensor, b_of
     dt = softplus(dt_pre[t, c]); S[n] <- exp(dt A[c, n]) S[n] + dt u[t, c] B_t[n]; y = sum_n S[n] C_t[n] + d[c] u[t, c];
     out[t, c] = y * silu(z[t, c]).  ``u`` [T, C] (the convolution's output), ``dt_pre`` float32 [T, C], B_t and C_t the
     ``n_states`` columns of ``bc``'s rows from ``b_off`` and ``c_off`` on, ``z`` and ``x`` [T, C] (column slices
-    allowed; x: the convolution's inputs), ``a_t`` float32 [N, C] (A transposed), ``d`` float32 [C].  The state
+    allowed; x: the convolution's inputs), ``a_t`` float32 [N, C] (A transposed and multiplied by log2(e): the kernel
+    takes exp2), ``d`` float32 [C].  The state
     [slots, taps - 1 + N, C] float32 holds the convolution's last inputs in its first taps - 1 rows and S behind them;
     both are left as they stand after the step's last token."""
     _cuda(u, "u"); _cuda(dt_pre, "dt_pre", torch.float32); _rows(bc, "bc"); _rows(z, "z"); _rows(x, "x")
@@ -919,40 +919,20 @@ def linear_attention_chunk() -> int:
     return int(_fn("linear_attention", "zlm_linear_attention_chunk")())
 
 
-def linear_attention_prep(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n_heads: int, dim: int, value_dim: int,
-                          rotary_dim: int, inv_freq: Optional[torch.Tensor], k_scale: float, positions: torch.Tensor,
-                          out: torch.Tensor) -> None:
-    """out (float32 [T, 2 * heads * dim + heads * value_dim], laid out [q | k | v]) = head h's q, k and v of ``proj``'s
-    rows (at q_off + h*dim, k_off + h*dim, v_off + h*value_dim), with the first ``rotary_dim`` dimensions of every q
-    and k head turned by the token's position (dimension i together with i + rotary_dim/2, angle position *
-    inv_freq[i]; ``inv_freq`` None: not turned) and k times ``k_scale``: what enters a linear-attention recurrence
-    whose q and k carry rotary positions, in float32 from the read on."""
-    _rows(proj, "proj"); _cuda(out, "out", torch.float32); _cuda(positions, "positions", torch.int32)
-    T = proj.shape[0]
-    qk, hv = n_heads * dim, n_heads * value_dim
-    if out.shape != (T, 2 * qk + hv):
-        raise KernelError("linear_attention_prep: out must be float32 [T, 2 * heads * dim + heads * value_dim]")
-    if max(q_off, k_off) + qk > proj.shape[1] or v_off + hv > proj.shape[1] or min(q_off, k_off, v_off) < 0:
-        raise KernelError("linear_attention_prep: the heads lie outside the rows")
-    if inv_freq is not None:
-        _cuda(inv_freq, "inv_freq", torch.float32)
-        if inv_freq.numel() * 2 != rotary_dim or rotary_dim > dim:
-            raise KernelError("linear_attention_prep: the frequency table must hold rotary_dim/2 entries")
-    _check(_fn("linear_attention", "zlm_linear_attention_prep")(
-        proj.data_ptr(), code(proj.dtype), _row_stride(proj), q_off, k_off, v_off, n_heads, dim, value_dim,
-        int(rotary_dim) if inv_freq is not None else 0, _ptr(inv_freq), float(k_scale), positions.data_ptr(),
-        out.data_ptr(), T, _stream()), "linear_attention_prep")
-
-
 def decayed_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, n_heads: int, dim: int,
                              value_dim: int, activation: Optional[str], pows: torch.Tensor, state: torch.Tensor, step,
-                             out: torch.Tensor) -> None:
+                             out: torch.Tensor, rotary_dim: int = 0, inv_freq: Optional[torch.Tensor] = None,
+                             key_scale: float = 1.0) -> None:
     """Linear attention with a fixed decay per head over the step's sequences: per head S <- a S + k v^T (float32
     [dim, value_dim], carried in ``state`` [slots, n_heads, dim, value_dim]) and o = S^T q.  Head h's q, k, v are the
     columns q_off + h*dim, k_off + h*dim, v_off + h*value_dim of ``proj``'s rows, read through ``activation``
     (None or "silu").  ``pows`` float32 [n_heads, chunk + 1]: decay_h^n.  ``out`` float32 [T, n_heads * value_dim].
     A step with a sequence of more tokens than a segment runs its segments side by side, with their start states in
-    the step's scratch; a step of one token a sequence updates the state in place."""
+    the step's scratch; a step of one token a sequence updates the state in place.  ``inv_freq`` (float32
+    [rotary_dim / 2]): q and k carry rotary positions, the first ``rotary_dim`` dimensions of every head turned by the
+    token's position (dimension i together with i + rotary_dim/2, angle position * inv_freq[i]); ``key_scale``: k times
+    a factor behind the rotation.  Both are applied to the float32 copies the kernel works on, so what enters the
+    recurrence is not rounded again."""
     _rows(proj, "proj"); _rows(out, "out"); _cuda(pows, "pows", torch.float32); _cuda(state, "state", torch.float32)
     T = proj.shape[0]
     if activation not in (None, "silu"):
@@ -966,13 +946,21 @@ def decayed_linear_attention(proj: torch.Tensor, q_off: int, k_off: int, v_off: 
         raise KernelError("decayed_linear_attention: the state must be [slots, heads, dim, value_dim]")
     if tuple(pows.shape) != (n_heads, linear_attention_chunk() + 1) or not pows.is_contiguous():
         raise KernelError("decayed_linear_attention: the table of powers must be [heads, chunk + 1]")
+    if inv_freq is not None:
+        _cuda(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() * 2 != rotary_dim or rotary_dim > dim:
+            raise KernelError("decayed_linear_attention: the frequency table must hold rotary_dim/2 entries, at most dim/2")
+        if activation is not None:
+            raise KernelError("decayed_linear_attention: an activation is not combined with a rotation")
     seg_state = None
     if not step.single_token and step.max_new > int(_fn("linear_attention", "zlm_linear_attention_segment")()):
         n = int(_fn("linear_attention", "zlm_linear_attention_segments")(T, step.n_seqs))
         seg_state = step.ws.buf("lin_segment_states", (n, n_heads, dim, value_dim), torch.float32)
     _check(_fn("linear_attention", "zlm_decayed_linear_attention")(
         proj.data_ptr(), code(proj.dtype), _row_stride(proj), q_off, k_off, v_off, n_heads, dim, value_dim,
-        1 if activation == "silu" else 0, pows.data_ptr(), state.data_ptr(), step.slots.data_ptr(),
+        1 if activation == "silu" else 0, int(rotary_dim) if inv_freq is not None else 0, _ptr(inv_freq),
+        step.positions.data_ptr() if inv_freq is not None else None, float(key_scale), pows.data_ptr(), state.data_ptr(),
+        step.slots.data_ptr(),
         step.cu_seqlens.data_ptr(), step.n_seqs, T, 1 if step.single_token and T == step.n_seqs else 0, _ptr(seg_state),
         out.data_ptr(), _row_stride(out), _stream()),
         "decayed_linear_attention")

@@ -8,8 +8,8 @@ For the rows h the mixer reads, H heads of query/key size D and value size V, de
 Options beside these: ``MixerSpec.position`` (rotary positions on q and k: the first rotated dimensions of every
 head are turned before the recurrence), ``key_scale`` (k times a factor, after the rotation), ``norm`` "heads" (the
 default: the heads normed together with the weight ``norm.weight``) or "head" (every head divided by its own root
-mean square, no weight), ``gate`` "sigmoid", "silu" (g * sigmoid(g)) or None.  With a rotation or a factor on k the
-rotated q, the rotated and scaled k and v go to the recurrence as float32 rows made by one kernel.
+mean square, no weight), ``gate`` "sigmoid", "silu" (g * sigmoid(g)) or None.  The rotation and the factor on k are
+applied to the float32 copies of q and k the recurrence's kernel works on.
 There is no other factor on the scores and no softmax.  A sequence carries [H, D, V] float32 from step to step
 (``StateNeed``); the recurrence, the scores q . k with their decays and the outputs are float32 in both precisions
 (the kernel works through a step in chunks of tokens, a decoded token being a chunk of one).  The four projections of
@@ -108,14 +108,11 @@ class DecayedLinearAttention(Part):
         proj = step.ws.buf("lin_proj", (T, 2 * qk + hv + (hv if self.gate else 0)), self.dtype)
         self.proj(h, proj)
         mixed = step.ws.buf("lin_mixed", (T, hv), torch.float32)
-        rows = proj
-        if self.prepared:
-            # rotated q, rotated and scaled k, and v as float32 rows: nothing that enters the recurrence is rounded again
-            rows = step.ws.buf("lin_prepared", (T, 2 * qk + hv), torch.float32)
-            table = self.position.rotary_table()
-            inv_freq, rot = table if table is not None else (None, 0)
-            kernels.linear_attention_prep(proj, 0, qk, 2 * qk, H, D, V, rot, inv_freq, self.key_scale, step.positions, rows)
-        kernels.decayed_linear_attention(rows, 0, qk, 2 * qk, H, D, V, self.activation, self.pows, io.state, step, mixed)
+        # a rotation and a factor on k are applied to the kernel's own float32 copies of q and k
+        table = self.position.rotary_table()
+        inv_freq, rot = table if table is not None else (None, 0)
+        kernels.decayed_linear_attention(proj, 0, qk, 2 * qk, H, D, V, self.activation, self.pows, io.state, step, mixed,
+                                         rotary_dim=rot, inv_freq=inv_freq, key_scale=self.key_scale)
         out = step.ws.buf("lin_out", (T, hv), self.dtype)
         gate = proj[:, 2 * qk + hv:] if self.gate else None
         if self.norm_kind == "heads" and self.gate != "silu":

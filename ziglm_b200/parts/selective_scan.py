@@ -16,6 +16,7 @@ Options of the spec: ``channels``, ``states``, ``taps``, ``dt_rank``.
 """
 from __future__ import annotations
 
+import math
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -59,7 +60,8 @@ class SelectiveScan(Part):
         self.o = Linear(tensors["o.weight"])
         self.conv_w = tensors["conv.weight"].float().t().contiguous()          # [taps, channels]: a row per tap
         self.conv_b = tensors["conv.bias"].float().contiguous()
-        self.a_t = (-torch.exp(tensors["A_log"].float())).t().contiguous()     # [states, channels]
+        # [states, channels], times log2(e): the kernel's exp(dt A) is one multiplication and one exp2
+        self.a_t = (-torch.exp(tensors["A_log"].float()) * math.log2(math.e)).t().contiguous()
         self.d = tensors["D"].float().contiguous()
 
     def kernel_libraries(self) -> Tuple[str, ...]:
