@@ -69,11 +69,24 @@ route_kernel(const float* __restrict__ z, long z_stride, const TH* __restrict__ 
             const TH* we = w + (long)e * d;
             float acc = 0.f;
             if (wide) {
-                for (int i = lane * V; i < d; i += 32 * V) {
-                    const uint4 raw = *reinterpret_cast<const uint4*>(we + i);
-                    const TH* wv = reinterpret_cast<const TH*>(&raw);
+                // four vectors of the row are requested before the first is used: with a handful of blocks the
+                // product is bound by the latency of its loads, not by their number
+                for (int i0 = lane * V; i0 < d; i0 += 4 * 32 * V) {
+                    uint4 raw[4];
 #pragma unroll
-                    for (int k = 0; k < V; ++k) acc = fmaf(row[i + k], to_float(wv[k]), acc);
+                    for (int u = 0; u < 4; ++u) {
+                        const int i = i0 + u * 32 * V;
+                        raw[u] = i < d ? *reinterpret_cast<const uint4*>(we + i) : make_uint4(0u, 0u, 0u, 0u);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int i = i0 + u * 32 * V;
+                        if (i < d) {
+                            const TH* wv = reinterpret_cast<const TH*>(&raw[u]);
+#pragma unroll
+                            for (int k = 0; k < V; ++k) acc = fmaf(row[i + k], to_float(wv[k]), acc);
+                        }
+                    }
                 }
             } else {
                 for (int i = lane; i < d; i += 32) acc = fmaf(row[i], to_float(we[i]), acc);
@@ -443,6 +456,47 @@ __global__ void combine_kernel(const float* __restrict__ y, const float* __restr
     out[idx] = accumulate ? out[idx] + acc : acc;
 }
 
+// The same sum, four elements of a row a thread (d a multiple of 4, rows of y, shared and out on 16-byte boundaries):
+// a pair's weight, expert and place are read once for the four.  Element by element the same arithmetic in the same order.
+template <typename TH>
+__global__ void combine_vec_kernel(const float* __restrict__ y, const float* __restrict__ weights, const int* __restrict__ place,
+                                   const int* __restrict__ ids, int n_real, const TH* __restrict__ h, long h_stride,
+                                   const float* __restrict__ shared, const float* __restrict__ gate, long gate_stride,
+                                   float* __restrict__ out, long total4, int d, int top, int accumulate) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total4) return;
+    const int d4 = d >> 2;
+    const long t = idx / d4;
+    const int i = (int)(idx % d4) * 4;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top; ++k) {
+        const long p = t * top + k;
+        const float w = weights[p];
+        if (ids != nullptr && ids[p] >= n_real) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] = fmaf(w, to_float(h[t * h_stride + i + e]), acc[e]);
+        } else {
+            const float4 v = *reinterpret_cast<const float4*>(y + (place ? (long)place[p] : p) * d + i);
+            acc[0] = fmaf(w, v.x, acc[0]); acc[1] = fmaf(w, v.y, acc[1]);
+            acc[2] = fmaf(w, v.z, acc[2]); acc[3] = fmaf(w, v.w, acc[3]);
+        }
+    }
+    if (shared != nullptr) {
+        const float g = gate ? 1.0f / (1.0f + expf(-gate[t * gate_stride])) : 1.0f;
+        const float4 v = *reinterpret_cast<const float4*>(shared + t * d + i);
+        acc[0] = fmaf(g, v.x, acc[0]); acc[1] = fmaf(g, v.y, acc[1]);
+        acc[2] = fmaf(g, v.z, acc[2]); acc[3] = fmaf(g, v.w, acc[3]);
+    }
+    float4* o = reinterpret_cast<float4*>(out + t * d + i);
+    if (accumulate) {
+        const float4 v = *o;
+        acc[0] = v.x + acc[0]; acc[1] = v.y + acc[1]; acc[2] = v.z + acc[2]; acc[3] = v.w + acc[3];
+    }
+    *o = make_float4(acc[0], acc[1], acc[2], acc[3]);
+}
+
 }  // namespace zlm
 
 using namespace zlm;
@@ -564,6 +618,17 @@ ZLM_EXPORT int zlm_moe_combine(const float* y, const float* weights, const int* 
     if (d <= 0 || top <= 0 || (ids != nullptr && h == nullptr)) return ZLM_ERR_BAD_ARG;
     const long total = (long)T * d;
     cudaError_t e;
+    if (d % 4 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)shared % 16 == 0) {
+        const long total4 = total / 4;
+        const unsigned blocks = (unsigned)((total4 + 255) / 256);
+        if (h_dtype == ZLM_BF16 && ids != nullptr)
+            e = launch_pdl(combine_vec_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, y, weights, place, ids, n_real,
+                           (const __nv_bfloat16*)h, h_stride, shared, gate, gate_stride, out, total4, d, top, accumulate);
+        else
+            e = launch_pdl(combine_vec_kernel<float>, dim3(blocks), dim3(256), 0, stream, y, weights, place, ids, n_real,
+                           (const float*)h, h_stride, shared, gate, gate_stride, out, total4, d, top, accumulate);
+        return e == cudaSuccess ? launch_status() : (int)e;
+    }
     if (h_dtype == ZLM_BF16 && ids != nullptr)
         e = launch_pdl(combine_kernel<__nv_bfloat16>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, y, weights,
                        place, ids, n_real, (const __nv_bfloat16*)h, h_stride, shared, gate, gate_stride, out, total, d, top,
