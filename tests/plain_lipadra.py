@@ -93,7 +93,8 @@ def same_chunk(query_pos: torch.Tensor, key_pos: torch.Tensor, size: Optional[in
 
 
 def softmax_one_more(s: torch.Tensor, seen: torch.Tensor) -> torch.Tensor:
-    """p_j = exp(s_j) / (1 + sum over the seen j of exp(s_j)): a sink with score 0 that has no value."""
+    """p_j = exp(s_j) / (1 + sum over the seen j of exp(s_j)): the denominator counts one more key, of score zero, that
+    carries nothing."""
     s = s.masked_fill(~seen, float("-inf"))
     m = torch.clamp(s.max(dim=-1, keepdim=True).values, min=0.0)
     e = torch.exp(s - m)

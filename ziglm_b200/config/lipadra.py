@@ -9,7 +9,7 @@ mixer is one of three:
                 head's length (one for all query heads, one for all key heads) before the rotation; rotary positions
                 over the first part of each head, dimension i paired with i + dims/2; a query sees the earlier keys
                 of its own chunk of ``mask.size`` positions only, chunks counted from the start of the sequence; the
-                softmax's denominator holds one more 1 (a sink of score 0 without a value).
+                softmax's denominator holds one more 1 (as if one more key of score zero that carries nothing were always seen).
 ``retention``   linear attention with a fixed decay per head: rotated q and k, k times dim^(-1/2) after the rotation,
                 S <- a S + k v^T, o = S^T q, every head's o divided by its own root mean square (no weight), the
                 heads times silu(W_g h).
