@@ -390,6 +390,7 @@ grouped_skinny_kernel(const TX* __restrict__ x, long x_stride, const TX* __restr
                 if (GLU) load16<TX>(we + u_row * K + k, wu);
 #pragma unroll
                 for (int r = 0; r < SK_ROWS; ++r) {
+                    if (r >= rows) break;               // the same for the whole block: a decode step's expert has a row or two
                     float xv[V];
                     load16<TX>(xs + (long)r * K + k, xv);
 #pragma unroll
@@ -401,9 +402,10 @@ grouped_skinny_kernel(const TX* __restrict__ x, long x_stride, const TX* __restr
             }
 #pragma unroll
             for (int r = 0; r < SK_ROWS; ++r) {
+                if (r >= rows) break;
                 const float g = warp_sum(acc[0][r]);
                 const float u = GLU ? warp_sum(acc[GLU ? 1 : 0][r]) : 0.f;
-                if (lane == 0 && r < rows) {
+                if (lane == 0) {
                     if (GLU) {
                         const float gr = round_to<TX>(g), ur = round_to<TX>(u);
                         ((TX*)out_)[(long)row_out[r] * out_stride + n] = from_float<TX>(expert_glu(gr, ur, glu_limit, glu_slope));
