@@ -23,7 +23,6 @@ T tokens of one sequence, C channels, N states a channel, K taps, E real experts
 """
 from __future__ import annotations
 
-import math
 from typing import Any, Dict, List, Mapping, Optional
 
 import torch

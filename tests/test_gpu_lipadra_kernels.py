@@ -56,8 +56,10 @@ def _part(family, spec, dtype, seed=0, scale=0.2, tweak=None):
     part = cls(spec, dtype, torch.device(DEV))
     part.bind(w)
     kernels.require(part.kernel_libraries())
-    return part, {k.replace(".weight", "").replace(".bias", ".b").replace("_norm", ".norm").replace("shared_gate", "shared.sg"): v.cpu()
-                  for k, v in w.items()}
+    def name(k):
+        return k.replace(".weight", "").replace(".bias", ".b").replace("_norm", ".norm").replace("shared_gate", "shared.sg")
+
+    return part, {name(k): v.cpu() for k, v in w.items()}
 
 
 @pytest.mark.parametrize("dtype", TYPES)

@@ -97,7 +97,8 @@ def test_a_random_model_in_every_schedule_in_float32(seed):
 
     def close(got, wl, what):
         err = _rows_error(got, wl)
-        assert torch.isfinite(err).all() and err.max().item() < 1e-3, f"{what}: row {int(err.argmax())} differs by {err.max().item():.3g}"
+        assert torch.isfinite(err).all() and err.max().item() < 1e-3, \
+            f"{what}: row {int(err.argmax())} differs by {err.max().item():.3g}"
 
     for r, wl in zip(reqs, want):
         s = eng.alloc_slot()
@@ -159,4 +160,5 @@ def test_every_layer_of_a_random_model_alone_in_bfloat16(seed):
             err = d.pow(2).mean(dim=1).sqrt() / wl.float().pow(2).mean(dim=1).sqrt()
             assert torch.isfinite(err).all(), f"layer {i}: a row is not finite"
             assert err.median().item() < 0.01 and int((err > 0.03).sum()) <= max(2, T // 25), \
-                f"layer {i} ({cfg['layers'][i]['type']}), {T} tokens: {int((err > 0.03).sum())} rows differ, median {err.median().item():.3g}"
+                f"layer {i} ({cfg['layers'][i]['type']}), {T} tokens: {int((err > 0.03).sum())} rows differ, " \
+                f"median {err.median().item():.3g}"

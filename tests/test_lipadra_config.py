@@ -39,7 +39,8 @@ def test_layout_schedule_and_names():
                    "l2.mlp.shared.gate", "l2.mlp.shared.sg", "l2.mix.norm", "l2.mix.q.b", "l0.mix.sink", "l0.mix.g"):
         assert absent not in names, absent
     att, scan, ret, causal = (l.mixer for l in spec.layers)
-    assert (att.options["chunk"], att.options["sink"], att.options["qk_norm"], att.window, att.bias) == (7, "zero", "head_first", None, True)
+    assert (att.options["chunk"], att.options["sink"], att.options["qk_norm"]) == (7, "zero", "head_first")
+    assert att.window is None and att.bias
     assert causal.options["chunk"] is None and causal.position.rotary_dim == 2
     assert scan.options == {"channels": 52, "states": 5, "taps": 3, "dt_rank": 3}
     assert ret.options["decay"] == (0.5, 0.9, 1.0) and ret.options["key_scale"] == 12 ** -0.5
@@ -110,10 +111,10 @@ def test_the_plain_parts_on_known_answers():
     assert torch.allclose(p, torch.tensor([[0.5, 0.0]]))
     p = P.softmax_one_more(torch.tensor([[math.log(3.0), math.log(4.0)]]), torch.tensor([[True, True]]))
     assert torch.allclose(p, torch.tensor([[3 / 8, 4 / 8]]))
-    # rotation of halves: a quarter turn takes (1, 0) to (0, 1) in the pair (0, 2); dimensions 4.. pass
+    # rotation of halves at position 1: the pair (0, 2) turns by one radian, the pair (1, 3) by base^(-1/2); 4.. pass
     x = torch.tensor([[[1.0, 2.0, 0.0, 0.0, 7.0]]])
     r = P.rotate_halves(x, torch.tensor([1]), {"dims": 4, "base": (math.pi / 2) ** -2})
-    a1 = (math.pi / 2) ** 1.0 * 1.0          # the second pair's frequency is base^(-2/4) = pi/2... times position 1
+    a1 = math.pi / 2                         # base = (pi/2)^-2, so the second pair's angle is a quarter turn
     assert torch.allclose(r[0, 0, [0, 2, 4]], torch.tensor([math.cos(1.0), math.sin(1.0), 7.0]), atol=1e-6)
     assert torch.allclose(r[0, 0, [1, 3]], torch.tensor([2 * math.cos(a1), 2 * math.sin(a1)]), atol=1e-6)
     # the router: groups are scored by their largest choice score, which may be negative; the weights carry no offset
@@ -145,7 +146,7 @@ def test_the_plain_implementation_in_portions(name):
     cfg = LC.config(name)
     conf = config_from_dict(cfg)
     g = torch.Generator().manual_seed(5)
-    w = {n: torch.randn(*d.shape, generator=g) * (0.2 if d.init == "normal" else 0.0) + (1.0 if d.init == "ones" else 0.0)
+    w = {n: torch.randn(*d.shape, generator=g) * 0.2 if d.init == "normal" else torch.ones(d.shape)
          for n, d in declare_parameters(conf.model_spec()).items()}
     LC.lively(w)
     plain = P.PlainLipadra(cfg, w, wide=True)
