@@ -74,7 +74,14 @@ _C = [
     {"type": "attention", "mixer": _att(5, 1, 10, 10, 0.4, 6, 300.0, 48), "mlp": _moe(9, 0, 4, 1.0, 12, (3, 2), 10)},
 ]
 CFG_C = _model(61, 40, 1e-6, 1.0, _C)
-CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C}
+# no size a multiple of 8: width, vocabulary, heads, channels, states, ranks, experts' widths
+_D = [
+    {"type": "attention", "mixer": _att(5, 1, 12, 6, 0.3, 6, 50.0, 9), "mlp": _moe(3, 2, 2, 1.3, 20, None, 12)},
+    {"type": "retention", "mixer": _ret(3, 10, 14, [0.95, 1.0, 0.7], 10, 300.0), "mlp": _moe(5, 1, 3, 0.9, 18, (3, 2), None)},
+    {"type": "mamba1", "mixer": _ssm(50, 6, 2, 5), "mlp": _moe(2, 0, 1, 1.0, 26, None, 10)},
+]
+CFG_D = _model(97, 52, 1e-5, 2.5, [_D[0], _D[1], _D[2], _shared(_D[1], 1)])
+CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D}
 
 
 def config(name: str) -> dict:

@@ -119,6 +119,25 @@ def test_float32_logits_do_not_depend_on_the_batch_beyond_rounding(zoo, name):
     assert (torch.cat([a, b]) - whole).abs().max().item() <= 5e-5 * whole.abs().max().item()
 
 
+@pytest.mark.parametrize("dn", DTYPES)
+def test_sizes_that_are_no_multiple_of_eight(zoo, dn):
+    """Width 52, vocabulary 97, heads of 12 and 10 with values of 6 and 14, 50 channels of 6 states: whole prompts, a
+    prompt then token by token, and portions."""
+    eng, cfg, w, reqs, want = zoo.get("D", dn)
+    for r, wl in zip(reqs, want):
+        s = eng.alloc_slot()
+        got = eng.step([(s, r)], [list(range(len(r)))]).clone()
+        eng.free_slot(s)
+        LC.rows_close(got, wl, dn, f"D whole, {len(r)} tokens")
+    r, wl = reqs[5], want[5]
+    s = eng.alloc_slot()
+    rows = [eng.step([(s, r[:31])], [list(range(31))]).clone(), eng.step([(s, r[31:33])], [[0, 1]]).clone()]
+    rows += [eng.step([(s, [t])]).clone() for t in r[33:]]
+    eng.free_slot(s)
+    LC.rows_close(torch.cat(rows), wl, dn, "D in portions, then one by one")
+    eng.cache.slots.check()
+
+
 def _one_layer(layer, vocab=90, width=64, alpha=1.0):
     return {"architecture": "Lipadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "postln_alpha": alpha,
             "layers": [layer]}
