@@ -187,13 +187,41 @@ constexpr int SS_MAX_N = 256;       // states a channel, when their number is no
 // chunks a block cuts a sequence into: as many as the registers of a thread's states allow threads
 constexpr int ss_max_chunks(int ns) { return ns > 0 && ns <= 16 ? 16 : 8; }
 
-template <typename T, int NS>
-__global__ void __launch_bounds__(SS_CH * ss_max_chunks(NS))
+// Eight consecutive numbers of a row as floats: sixteen bytes at a time where the row allows it (``wide``: the address
+// is a multiple of 16 bytes for every token), else one by one.  The same for all threads of a warp: a broadcast.
+__device__ __forceinline__ void ss_load8(const float* __restrict__ p, float (&f)[8], bool wide) {
+    if (wide) {
+        const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+        f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = p[i];
+    }
+}
+__device__ __forceinline__ void ss_load8(const __nv_bfloat16* __restrict__ p, float (&f)[8], bool wide) {
+    if (wide) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 v = __bfloat1622float2(h[i]);
+            f[2 * i] = v.x; f[2 * i + 1] = v.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(p[i]);
+    }
+}
+
+// ROOMY: the grid has no more blocks than the GPU has SMs, so a block may have an SM's registers to itself (no spills,
+// more loads in flight); else two blocks share an SM (but for 64 states, whose registers fill one).
+template <typename T, int NS, bool ROOMY>
+__global__ void __launch_bounds__(SS_CH * ss_max_chunks(NS), (NS == 64 || ROOMY) ? 1 : 2)
 selective_scan_kernel(const T* __restrict__ u, const float* __restrict__ dtp, const T* __restrict__ bc, long bc_stride,
                       int b_off, int c_off, const T* __restrict__ z, long z_stride, const T* __restrict__ x,
                       long x_stride, const float* __restrict__ a2_t, const float* __restrict__ dvec,
                       float* __restrict__ state, long state_stride, const int* __restrict__ cu_seqlens,
-                      const int* __restrict__ slots, T* __restrict__ out, int C, int N_rt, int K) {
+                      const int* __restrict__ slots, T* __restrict__ out, int C, int N_rt, int K, int wide) {
     extern __shared__ float ss_sm[];
     constexpr int NA = NS > 0 ? NS : SS_MAX_N;
     const int N = NS > 0 ? NS : N_rt;
@@ -221,14 +249,30 @@ selective_scan_kernel(const T* __restrict__ u, const float* __restrict__ dtp, co
         if (live) {
 #pragma unroll (NS > 0 ? NS : 1)
             for (int n = 0; n < N; ++n) S[n] = 0.f;
+            // the step size and the input of the next token are requested before this token's arithmetic begins
+            float dtp_next = lo < hi ? dtp[(long)lo * C + c] : 0.f;
+            float u_next = lo < hi ? to_float(u[(long)lo * C + c]) : 0.f;
             for (int t = lo; t < hi; ++t) {
-                const float dt = softplus_f(dtp[(long)t * C + c]);
-                const float dx = dt * to_float(u[(long)t * C + c]);
+                const float dt = softplus_f(dtp_next);
+                const float dx = dt * u_next;
+                if (t + 1 < hi) {
+                    dtp_next = dtp[(long)(t + 1) * C + c];
+                    u_next = to_float(u[(long)(t + 1) * C + c]);
+                }
                 const T* bt = bc + (long)t * bc_stride + b_off;
                 dt_sum += dt;
-#pragma unroll (NS > 0 ? NS : 1)
-                for (int n = 0; n < N; ++n)
-                    S[n] = fmaf(exp2f(dt * A[n]), S[n], dx * to_float(bt[n]));
+                if constexpr (NS > 0) {
+#pragma unroll
+                    for (int n0 = 0; n0 < NS; n0 += 8) {
+                        float b8[8];
+                        ss_load8(bt + n0, b8, wide != 0);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) S[n0 + i] = fmaf(exp2f(dt * A[n0 + i]), S[n0 + i], dx * b8[i]);
+                    }
+                } else {
+                    for (int n = 0; n < N; ++n)
+                        S[n] = fmaf(exp2f(dt * A[n]), S[n], dx * to_float(bt[n]));
+                }
             }
 #pragma unroll (NS > 0 ? NS : 1)
             for (int n = 0; n < N; ++n)
@@ -250,19 +294,37 @@ selective_scan_kernel(const T* __restrict__ u, const float* __restrict__ dtp, co
     }
     // pass 2: the outputs
     const float dc = dvec[c];
+    float dtp_next = lo < hi ? dtp[(long)lo * C + c] : 0.f;
+    float u_next = lo < hi ? to_float(u[(long)lo * C + c]) : 0.f;
     for (int t = lo; t < hi; ++t) {
-        const float dt = softplus_f(dtp[(long)t * C + c]);
-        const float uv = to_float(u[(long)t * C + c]);
+        const float dt = softplus_f(dtp_next);
+        const float uv = u_next;
         const float dx = dt * uv;
+        if (t + 1 < hi) {
+            dtp_next = dtp[(long)(t + 1) * C + c];
+            u_next = to_float(u[(long)(t + 1) * C + c]);
+        }
         const T* bt = bc + (long)t * bc_stride + b_off;
         const T* ct = bc + (long)t * bc_stride + c_off;
         float y = 0.f;
-#pragma unroll (NS > 0 ? NS : 1)
-        for (int n = 0; n < N; ++n)
-            {
+        if constexpr (NS > 0) {
+#pragma unroll
+            for (int n0 = 0; n0 < NS; n0 += 8) {
+                float b8[8], c8[8];
+                ss_load8(bt + n0, b8, wide != 0);
+                ss_load8(ct + n0, c8, wide != 0);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    S[n0 + i] = fmaf(exp2f(dt * A[n0 + i]), S[n0 + i], dx * b8[i]);
+                    y = fmaf(S[n0 + i], c8[i], y);
+                }
+            }
+        } else {
+            for (int n = 0; n < N; ++n) {
                 S[n] = fmaf(exp2f(dt * A[n]), S[n], dx * to_float(bt[n]));
                 y = fmaf(S[n], to_float(ct[n]), y);
             }
+        }
         y = fmaf(dc, uv, y);
         out[(long)t * C + c] = from_float<T>(y * silu_f(to_float(z[(long)t * z_stride + c])));
     }
@@ -360,11 +422,24 @@ ZLM_EXPORT int zlm_selective_scan(const void* u, int dtype, const float* dtp, co
     while (chunks > 1 && (size_t)chunks * (N + 1) * SS_CH * sizeof(float) > 48 * 1024) --chunks;
     const size_t smem = chunks > 1 ? (size_t)chunks * (N + 1) * SS_CH * sizeof(float) : 0;
     dim3 grid(n_seqs, (C + SS_CH - 1) / SS_CH), block(SS_CH, chunks);
+    // B and C of a token can be read sixteen bytes at a time when every token's B and C start on such a boundary
+    const int per16 = dtype == ZLM_F32 ? 4 : 8;
+    const int wide = (b_off % per16 == 0 && c_off % per16 == 0 && bc_stride % per16 == 0 && (uintptr_t)bc % 16 == 0) ? 1 : 0;
+    static int n_sms = 0;
+    if (n_sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            n_sms = 1;
+    }
+    const bool roomy = (long)grid.x * grid.y <= n_sms;
     cudaError_t e;
 #define ZLM_SS(TT, NS)                                                                                                \
-    e = launch_pdl(selective_scan_kernel<TT, NS>, grid, block, smem, stream, (const TT*)u, dtp, (const TT*)bc, bc_stride, \
-                   b_off, c_off, (const TT*)z, z_stride, (const TT*)x, x_stride, a2_t, dvec, state, state_stride, cu_seqlens, \
-                   slots, (TT*)out, C, N, K)
+    e = roomy ? launch_pdl(selective_scan_kernel<TT, NS, true>, grid, block, smem, stream, (const TT*)u, dtp, (const TT*)bc, \
+                           bc_stride, b_off, c_off, (const TT*)z, z_stride, (const TT*)x, x_stride, a2_t, dvec, state,   \
+                           state_stride, cu_seqlens, slots, (TT*)out, C, N, K, wide)                                     \
+              : launch_pdl(selective_scan_kernel<TT, NS, false>, grid, block, smem, stream, (const TT*)u, dtp, (const TT*)bc, \
+                           bc_stride, b_off, c_off, (const TT*)z, z_stride, (const TT*)x, x_stride, a2_t, dvec, state,   \
+                           state_stride, cu_seqlens, slots, (TT*)out, C, N, K, wide)
 #define ZLM_SS_N(TT)                                                                                                  \
     switch (N) {                                                                                                      \
         case 8: ZLM_SS(TT, 8); break;                                                                                 \
